@@ -4,7 +4,8 @@ from .specs import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec,
 from .qwen3 import Qwen3Config
 from .temetar import TemetarConfig
 from .movarax import MovaraxConfig
+from .linonex import LinonexConfig
 
 __all__ = ["ConfigError", "architecture_names", "architecture_of", "get_architecture", "load_config",
            "read_config_json", "register_architecture", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
-           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig", "MovaraxConfig"]
+           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig", "MovaraxConfig", "LinonexConfig"]

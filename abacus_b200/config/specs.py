@@ -49,6 +49,10 @@ class AttentionSpec:
     sequence's first F keys stay visible behind the window, at their true positions. sink: a learned score
     per query head (slot "sink") that joins the softmax's denominator once, unscaled, with no key and no value.
     exact_weights: the softmax's weights stay float32 in the second product also where the model is bfloat16.
+    conv_taps T > 0: q, k and v each pass a causal convolution of T taps per channel (no activation) right after their
+    projection (slots "conv_q", "conv_k", "conv_v", [channels, taps], the last tap the token's own); the last T - 1
+    projected rows are part of the sequence's state. chunk C: key j is seen from i only if i // C == j // C, positions
+    counted from the sequence's first token. softcap c: score <- c * tanh(score / c), after the scale.
     """
     hidden: int
     n_heads: int
@@ -62,6 +66,9 @@ class AttentionSpec:
     keep_first: int = 0
     sink: bool = False
     exact_weights: bool = False
+    conv_taps: int = 0
+    chunk: Optional[int] = None
+    softcap: Optional[float] = None
     kind: str = "attention"
 
 
@@ -88,6 +95,57 @@ class DeltaRuleSpec:
     norm_eps: float
     unit_eps: float = 1e-6
     kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class HeadDeltaSpec:
+    """A recurrent mixer: the gated delta rule with one decay per head.
+
+    As DeltaRuleSpec, but g = exp(-exp(A_h) * softplus(a_h . x + bias_h)) is one number a head (slot "wa", [heads, hidden]),
+    and the output gate is silu(G x) with G a full matrix [heads * value_dim, hidden].
+    """
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    kind: str = "head_delta"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """A recurrent mixer: a matrix memory per head with exponential gates kept in range by a running maximum.
+
+    Per head q = Wq x * key_dim^-1/2, k = Wk x, v = Wv x, and two gates in the log domain,
+        i = cap * tanh((wi . x + bi) / cap),    f = logsigmoid(cap * tanh((wf . x + bf) / cap)).
+    State C [key, value], n [key] and a scalar m, all zero at a sequence's start (m too):
+        m' = max(f + m, i);  C' = e^(f + m - m') C + e^(i - m') k v^T;  n' likewise with k alone;
+        o = C'^T q / (max(|n' . q|, e^(-m')) + denom_eps).
+    Each head's o is divided by its root mean square (norm_eps), the heads side by side are multiplied by a weight
+    [heads * value_dim] and by sigmoid(Wg x), then projected.
+    """
+    hidden: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    norm_eps: float
+    denom_eps: float = 1e-6
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is share * (norm(left(x); w_left) + norm(right(x); w_right)),
+    each output normed over the model's width with a plain weight of its own (slots "left_out", "right_out")."""
+    hidden: int
+    left: object
+    right: object
+    norm_eps: float
+    share: float = 0.5
+    kind: str = "side_by_side"
 
 
 @dataclass(frozen=True)
@@ -134,7 +192,7 @@ class DecayAttentionSpec:
 
 @dataclass(frozen=True)
 class ExpertSpec:
-    """A small feed-forward without a gate: down(act(up(x)))."""
+    """A small feed-forward: down(act(up(x))), or, with activation "silu_gated", down(silu(gate(x)) * up(x))."""
     inter: int
     activation: str = "relu_squared"
 
@@ -144,9 +202,12 @@ class RoutedMLPSpec:
     """A feed-forward of `experts` small layers of which each token uses `top`, and an optional shared one.
 
     Router logits z = R x in float32; score "sigmoid": s = sigmoid(z), the `top` largest chosen, weights the chosen s
-    as they are; score "softmax_chosen": the softmax of the chosen logits. weight_on "input": the output is
-    sum_e expert_e(w_e x); "output": sum_e w_e expert_e(x). shared (an ExpertSpec or None) runs for every token and
-    is added.
+    as they are; score "softmax_chosen": the softmax of the chosen logits; score "softmax_all": s = softmax(z) over
+    all router outputs, the choice goes by s (plus, with correction, a learned shift per output, slot "correction", that
+    the weights do not see) and the weights are the chosen s * weight_scale, not renormalized. identity I: the router has
+    experts + I outputs, and the last I stand for experts without tensors whose output is their input.
+    weight_on "input": the output is sum_e expert_e(w_e x); "output": sum_e w_e expert_e(x). shared (an ExpertSpec or
+    None) runs for every token and is added.
     """
     hidden: int
     experts: int
@@ -155,6 +216,9 @@ class RoutedMLPSpec:
     shared: Optional[ExpertSpec] = None
     score: str = "sigmoid"
     weight_on: str = "input"
+    correction: bool = False
+    weight_scale: float = 1.0
+    identity: int = 0
     kind: str = "routed_mlp"
 
 
@@ -216,15 +280,27 @@ class PairEmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class PositionEmbeddingSpec:
+    """The frame "positions": x = table[token] + positions[position], a learned vector per position (slot "positions",
+    [max_positions, hidden]), not scaled. keep: the frame keeps x as it leaves the embedding, for schedule entries that
+    add it to the stream again (ScheduleEntry.rejoin)."""
+    max_positions: int
+    keep: bool = False
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One entry of the run order.
 
     layer: index into ModelSpec.layers (a layer may be named more than once).
     source: None if the mixer keeps keys/values or state of its own for this
     entry; else the index of an earlier entry whose cache it reads.
+    rejoin: right before this entry runs, what the frame kept of the embedding is added to the stream (the frame
+    must keep it).
     """
     layer: int
     source: Optional[int] = None
+    rejoin: bool = False
 
 
 @dataclass(frozen=True)

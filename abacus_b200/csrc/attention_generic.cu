@@ -5,7 +5,9 @@
 // the tensor-core kernels, and summed unrounded; a model that wants them in float32 says so).
 // Options: values of another size than keys; a window that also keeps a sequence's first keys (key j is
 // seen from i when j <= i and (i - j < window or j < keep_first)); a sink, a learned score per head that
-// joins the softmax's denominator once, unscaled, without a key or a value.
+// joins the softmax's denominator once, unscaled, without a key or a value; chunks (key j is seen from i only when
+// both lie in the same run of `chunk` positions, counted from the sequence's first); capped scores
+// (s <- cap * tanh(s / cap), after the scale).
 // It serves prefill and decode alike and is the kernel every size falls back to; the float32
 // path of the model uses nothing else for attention.
 //
@@ -41,6 +43,8 @@ struct AttnGeneric {
     PagedCache v_cache; // the values' pool has pages of v_dim
     int values_in_keys; // a value is the first v_dim elements of its key (one pool, one row per token)
     int vector_rows;    // key rows are whole 16-byte pieces at 16-byte places (else they are read an element at a time)
+    int chunk;          // > 0: only the keys of the token's own run of `chunk` positions are seen
+    float softcap;      // > 0: s <- softcap * tanh(s / softcap)
 };
 
 template <typename T> __device__ __forceinline__ float dot_row_plain(const float *q, const T *k, int hd) {
@@ -90,6 +94,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
     int pos = p.token_pos[t], slot = p.seq_slot[seq];
     int kvh = h / (p.n_heads / p.n_kv_heads);
     int lo = p.window > 0 && pos - p.window + 1 > 0 ? pos - p.window + 1 : 0;
+    if (p.chunk > 0 && pos / p.chunk * p.chunk > lo) lo = pos / p.chunk * p.chunk;
     // the sequence's first keys that the window no longer reaches: positions [0, first_end)
     int first_end = p.keep_first < lo ? p.keep_first : lo;
     const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)h * hd;
@@ -119,8 +124,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
                 k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
             }
             v_off[tid] = vo;
-            s = (p.vector_rows ? dot_row<T>(q_s, k, hd) : dot_row_plain<T>(q_s, k, hd)) *
-                (ROUNDED_P ? p.scale * 1.4426950408889634f : p.scale);
+            s = (p.vector_rows ? dot_row<T>(q_s, k, hd) : dot_row_plain<T>(q_s, k, hd)) * p.scale;
+            if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
+            if (ROUNDED_P) s *= 1.4426950408889634f;
         }
         float m_new, pj, corr;
         if (ROUNDED_P) {
@@ -166,9 +172,10 @@ static int attention_general(int values_in_keys, const void *q, long long q_row,
                                      const int *page_table, int table_width, int ring_pages, int tokens_per_page,
                                      const void *k_step, const void *v_step, long long kv_row, int v_dim,
                                      int keep_first, int pinned_pages, const float *sink, int exact_weights,
-                                     void *stream) {
+                                     void *stream, int chunk = 0, float softcap = 0.0f) {
     if (n_tokens <= 0) return 0;
     if (v_dim <= 0) v_dim = head_dim;
+    if (chunk < 0 || softcap < 0.0f) ABK_REFUSE("attention: a chunk of %d positions, a score cap of %g", chunk, softcap);
     if (v_dim > ATT_MAX_HEAD_DIM) ABK_REFUSE("attention: value size %d is more than %d", v_dim, ATT_MAX_HEAD_DIM);
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) keep_first = 0;
     if (sink && !exact_weights && dtype == ABK_BF16)
@@ -188,6 +195,7 @@ static int attention_general(int values_in_keys, const void *q, long long q_row,
     p.v_cache = p.cache;
     p.k_step = k_step, p.v_step = v_step, p.kv_row = kv_row;
     p.v_dim = v_dim, p.keep_first = keep_first, p.sink = sink, p.values_in_keys = values_in_keys;
+    p.chunk = chunk, p.softcap = softcap;
     if (values_in_keys && v_dim > head_dim) ABK_REFUSE("attention: values of %d inside keys of %d", v_dim, head_dim);
     const int esize = dtype == ABK_BF16 ? 2 : 4;
     p.vector_rows = (head_dim * esize) % 16 == 0 && (kv_row * esize) % 16 == 0 &&
@@ -215,6 +223,21 @@ extern "C" int abk_attention_general(const void *q, long long q_row, void *out, 
                              token_pos, seq_slot, seq_start, seq_pos0, k_pool, v_pool, page_table, table_width, ring_pages,
                              tokens_per_page, k_step, v_step, kv_row, v_dim, keep_first, pinned_pages, sink, exact_weights,
                              stream);
+}
+
+// The general form with chunks and capped scores.
+extern "C" int abk_attention_chunked(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                     int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
+                                     const int *token_pos, const int *seq_slot, const int *seq_start,
+                                     const int *seq_pos0, const void *k_pool, const void *v_pool,
+                                     const int *page_table, int table_width, int ring_pages, int tokens_per_page,
+                                     const void *k_step, const void *v_step, long long kv_row, int v_dim,
+                                     int keep_first, int pinned_pages, const float *sink, int exact_weights, int chunk,
+                                     float softcap, void *stream) {
+    return attention_general(0, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, token_seq,
+                             token_pos, seq_slot, seq_start, seq_pos0, k_pool, v_pool, page_table, table_width, ring_pages,
+                             tokens_per_page, k_step, v_step, kv_row, v_dim, keep_first, pinned_pages, sink, exact_weights,
+                             stream, chunk, softcap);
 }
 
 // Keys that carry their values: a value is the first v_dim elements of its key row (one pool; with keys from the

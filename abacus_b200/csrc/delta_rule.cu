@@ -4,7 +4,8 @@
 // Per head, with a state S [key, value] in float32 that starts at zero and is carried from token to token:
 //     S <- diag(g) S;   e = b (v - S^T k);   S <- S + k e^T;   o = S^T q
 // q and k are unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times key^-1/2; b = sigmoid(.) per head;
-// g = exp(-exp(A) * softplus(a + bias)) per head and key channel. Everything that enters the recurrence is
+// g = exp(-exp(A) * softplus(a + bias)) per head and key channel (or, per_head, one for all of a head's channels).
+// The convolution may also stand alone, without its SiLU (plain). Everything that enters the recurrence is
 // float32; q, k and v come from the convolution in the model's storage type.
 //
 // A value column of S never meets another: column j needs S[:, j], v_j and the token's q, k, g, b. So a thread
@@ -30,6 +31,7 @@ struct ShortConv {
     int tokens_per_block;  // of the vector kernel: 4 for long steps (its weights read once for four tokens), 1 for short ones
     float *new_tail;       // a step of one token a sequence: the kernel leaves the slot's new tail itself (the thread that
                            // read a channel's old tail writes its new one); null: short_conv_tail does it
+    int plain;             // 1: the sum as it is, no SiLU behind it
 };
 
 template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(ShortConv p) {
@@ -56,7 +58,7 @@ template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(S
         if (left && j > 0) left[(long long)(j - 1) * p.channels] = v;  // the input `back` tokens ago is back + 1 ago next time
         acc = fmaf(w[j], v, acc);
     }
-    *out = from_float<T>(acc / (1.0f + expf(-acc)));
+    *out = from_float<T>(p.plain ? acc : acc / (1.0f + expf(-acc)));
 }
 
 // The same with VEC channels a thread (16 bytes of the storage type), for channel counts and row pitches that are
@@ -133,7 +135,7 @@ template <typename T, int VEC, int TAPS> __global__ void __launch_bounds__(128) 
                 for (int u = 0; u < VEC; u++) acc[u] = fmaf(w[u * TAPS + j], v[u], acc[u]);
             }
 #pragma unroll
-            for (int u = 0; u < VEC; u++) acc[u] = acc[u] / (1.0f + expf(-acc[u]));
+            for (int u = 0; u < VEC; u++) acc[u] = p.plain ? acc[u] : acc[u] / (1.0f + expf(-acc[u]));
         }
         ConvVector<T, VEC>::store(out, acc);
     }
@@ -142,13 +144,13 @@ template <typename T, int VEC, int TAPS> __global__ void __launch_bounds__(128) 
 // update_tail: every sequence of the step brings one token, and the kernel leaves the slots' new tails itself.
 extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype, const float *w, float *tail,
                               const int *token_seq, const int *token_pos, const int *seq_slot, const int *seq_pos0,
-                              int n_tokens, int channels, int taps, int update_tail, void *stream) {
+                              int n_tokens, int channels, int taps, int update_tail, int plain, void *stream) {
     if (n_tokens <= 0 || channels <= 0) return 0;
     if (taps < 1 || taps > CONV_MAX_TAPS) ABK_REFUSE("short convolution: %d taps, the kernel takes 1 to %d", taps, CONV_MAX_TAPS);
     ShortConv p;
     p.in = in, p.ld = ld, p.out = out, p.w = w, p.tail = tail, p.token_seq = token_seq, p.token_pos = token_pos;
     p.seq_slot = seq_slot, p.seq_pos0 = seq_pos0, p.channels = channels, p.taps = taps, p.n_tokens = n_tokens;
-    p.tokens_per_block = 1;
+    p.tokens_per_block = 1, p.plain = plain;
     p.new_tail = update_tail && taps > 1 ? tail : nullptr;
     dim3 grid(n_tokens, (channels + 127) / 128);
     if (grid.y > 65535) ABK_REFUSE("short convolution: %d channels are more than a grid takes", channels);
@@ -225,8 +227,9 @@ static inline int delta_record_floats(int key, int value) { return 3 * delta_par
 struct DeltaPrepare {
     const void *qkv;        // [tokens, ld_qkv]: q heads (kv_heads x key), k heads, v heads (heads x value), after the convolution
     long long ld_qkv;
-    const float *decay_in;  // row t at decay_in + t * ld_decay, heads * key: a, before bias and softplus
-    long long ld_decay;
+    const void *decay_in;   // row t at decay_in + t * ld_decay, heads * key float32: a, before bias and softplus; with
+    long long ld_decay;     // per_head: one a per head, `heads` of them in the storage type, and dt_bias [heads]
+    int per_head;
     const void *beta_in;    // row t, head h at beta_in[t * ld_beta + h], before the sigmoid
     long long ld_beta;
     const float *a_log;     // [heads]
@@ -254,6 +257,10 @@ template <typename T> __global__ void __launch_bounds__(128) delta_prepare_kerne
     const T *kr = qr + (long long)p.kv_heads * K;
     const T *vr = (const T *)p.qkv + row * p.ld_qkv + 2LL * p.kv_heads * K + (long long)h * V;
     const float rate = expf(p.a_log[h]);
+    float head_decay = 0.0f;  // one decay for all of the head's key channels
+    if (p.per_head)
+        head_decay = expf(-rate * softplus_f(to_float(((const T *)p.decay_in)[row * p.ld_decay + h]) + p.dt_bias[h]));
+    const float *channel_decay = (const float *)p.decay_in + row * p.ld_decay + (long long)h * K;
     float qq = 0.0f, kk = 0.0f;
     for (int i = lane; i < K; i += 32) {
         const float qv = to_float(qr[i]), kv = to_float(kr[i]);
@@ -266,7 +273,7 @@ template <typename T> __global__ void __launch_bounds__(128) delta_prepare_kerne
         const bool real = at % SCAN_RUN < SCAN_ROWS && i < K;
         rec[at] = real ? to_float(kr[i]) * kn : 0.0f;
         rec[region + at] = real ? to_float(qr[i]) * qn : 0.0f;
-        rec[2 * region + at] = real ? expf(-rate * softplus_f(p.decay_in[row * p.ld_decay + (long long)h * K + i] + p.dt_bias[h * K + i])) : 0.0f;
+        rec[2 * region + at] = !real ? 0.0f : p.per_head ? head_decay : expf(-rate * softplus_f(channel_decay[i] + p.dt_bias[h * K + i]));
     }
     const int vp = p.record - 3 * region - 4;
     for (int j = lane; j < vp; j += 32) rec[3 * region + j] = j < V ? to_float(vr[j]) : 0.0f;
@@ -426,7 +433,7 @@ extern "C" long long abk_delta_scan_scratch(int n_tokens, int heads, int key, in
     return (long long)n_tokens * heads * delta_record_floats(key, value);
 }
 
-extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const float *decay_in, long long ld_decay, const void *beta_in,
+extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const void *decay_in, long long ld_decay, int per_head, const void *beta_in,
                               long long ld_beta, const float *a_log, const float *dt_bias, float *state, float *out,
                               const int *token_seq, const int *seq_start, const int *seq_slot, int n_tokens, int n_seqs,
                               int heads, int kv_heads, int key, int value, float *records, long long records_floats,
@@ -449,7 +456,7 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
     if (smem > 220 * 1024) ABK_REFUSE("delta rule: heads of %d x %d need more shared memory than an SM has", key, value);
     cudaStream_t s = (cudaStream_t)stream;
     DeltaPrepare q;
-    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.ld_decay = ld_decay, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
+    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.ld_decay = ld_decay, q.per_head = per_head, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
     q.dt_bias = dt_bias, q.records = records, q.token_seq = token_seq, q.pairs = (long long)n_tokens * heads;
     q.heads = heads, q.kv_heads = kv_heads, q.key = key, q.value = value, q.parts = parts, q.record = record;
     q.q_scale = 1.0f / sqrtf((float)key);
@@ -480,37 +487,47 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
 }
 
 // ------------------------------------------------------------------ gated per-head norm
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :]); one warp per (token, head). A token's
-// gates lie at gate + t * ld_gate.
-template <typename T>
-__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float *o, const float *gate, long long ld_gate, int heads,
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]); one warp per (token, head). A token's
+// gates lie at gate + t * ld_gate, float32 or (TG) in the storage type. act: sigmoid, or (silu) z sigmoid(z). w: [value],
+// shared by the heads, or (w_per_head) [heads * value].
+template <typename T, typename TG>
+__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float *o, const TG *gate, long long ld_gate, int heads,
                                                               const float *w, T *out, long long n_heads_total, int value,
-                                                              float eps) {
+                                                              float eps, int silu, int w_per_head) {
     pdl_wait();
     const long long head = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (head >= n_heads_total) return;
-    const float *src = o + head * value, *gs = gate + (head / heads) * ld_gate + (head % heads) * value;
+    const float *src = o + head * value;
+    const TG *gs = gate + (head / heads) * ld_gate + (head % heads) * value;
+    if (w_per_head) w += (head % heads) * value;
     float ss = 0.0f;
     for (int j = lane; j < value; j += 32) ss = fmaf(src[j], src[j], ss);
     ss = warp_sum(ss);
     const float scale = 1.0f / sqrtf(ss / (float)value + eps);
-    for (int j = lane; j < value; j += 32)
-        out[head * value + j] = from_float<T>(src[j] * scale * w[j] * (1.0f / (1.0f + expf(-gs[j]))));
+    for (int j = lane; j < value; j += 32) {
+        const float z = to_float(gs[j]), sg = 1.0f / (1.0f + expf(-z));
+        out[head * value + j] = from_float<T>(src[j] * scale * w[j] * (silu ? z * sg : sg));
+    }
 }
 
-extern "C" int abk_gated_head_norm(const float *o, const float *gate, long long ld_gate, const float *w, void *out, int dtype,
-                                   int n_tokens, int heads, int value, float eps, void *stream) {
+extern "C" int abk_gated_head_norm(const float *o, const void *gate, long long ld_gate, int gate_stored, const float *w, void *out,
+                                   int dtype, int n_tokens, int heads, int value, float eps, int silu, int w_per_head,
+                                   void *stream) {
     const long long total = (long long)n_tokens * heads;
     if (total <= 0) return 0;
     const long long blocks = (total + 3) / 4;
     if (blocks > 0x7fffffffLL) ABK_REFUSE("gated norm: %lld heads are more than a grid takes", total);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == ABK_BF16)
-        abk_launch(gated_head_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, ld_gate, heads, w,
-                   (__nv_bfloat16 *)out, total, value, eps);
+    typedef __nv_bfloat16 bf;
+    if (dtype == ABK_BF16 && gate_stored)
+        abk_launch(gated_head_norm_kernel<bf, bf>, dim3((unsigned)blocks), dim3(128), 0, s, o, (const bf *)gate, ld_gate, heads, w,
+                   (bf *)out, total, value, eps, silu, w_per_head);
+    else if (dtype == ABK_BF16)
+        abk_launch(gated_head_norm_kernel<bf, float>, dim3((unsigned)blocks), dim3(128), 0, s, o, (const float *)gate, ld_gate, heads, w,
+                   (bf *)out, total, value, eps, silu, w_per_head);
     else
-        abk_launch(gated_head_norm_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, ld_gate, heads, w,
-                   (float *)out, total, value, eps);
+        abk_launch(gated_head_norm_kernel<float, float>, dim3((unsigned)blocks), dim3(128), 0, s, o, (const float *)gate, ld_gate, heads, w,
+                   (float *)out, total, value, eps, silu, w_per_head);
     return ABK_LAUNCH_RESULT();
 }

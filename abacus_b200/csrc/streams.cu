@@ -281,3 +281,87 @@ extern "C" int abk_remember_tokens(const int *tokens, const int *seq_start, cons
                seq_slot, n_seqs, remembered);
     return ABK_LAUNCH_RESULT();
 }
+
+// ------------------------------------------------------------------ learned positions, a stream that is joined again
+// x[t, a] = table[token] + positions[position] for every stream a: an embedding with a learned vector per position (not
+// scaled). `keep` (or null) gets a copy [tokens, d]: what a later layer adds to the stream again (rejoin).
+struct EmbedPositions {
+    const int *tokens, *token_seq, *token_pos;
+    const void *table, *positions;
+    float *x, *keep;
+    int d, vocab, n_positions, s;
+    int *status;
+};
+
+template <typename TW> __global__ void embed_positions_kernel(EmbedPositions p) {
+    pdl_wait();
+    const int t = blockIdx.x, d = p.d;
+    const int seq = p.token_seq[t];
+    float *out = p.x + (long long)t * p.s * d;
+    float *keep = p.keep ? p.keep + (long long)t * d : nullptr;
+    const int tok = seq < 0 ? 0 : p.tokens[t], pos = seq < 0 ? 0 : p.token_pos[t];
+    const bool bad = tok < 0 || tok >= p.vocab || pos < 0 || pos >= p.n_positions;
+    if (seq >= 0 && bad && threadIdx.x == 0) atomicOr(p.status, 1);
+    const TW *e = (const TW *)p.table + (long long)(bad ? 0 : tok) * d;
+    const TW *w = (const TW *)p.positions + (long long)(bad ? 0 : pos) * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = seq < 0 || bad ? 0.0f : to_float(e[j]) + to_float(w[j]);
+        for (int a = 0; a < p.s; a++) out[(long long)a * d + j] = v;
+        if (keep) keep[j] = v;
+    }
+}
+
+extern "C" int abk_embed_positions(const int *tokens, const int *token_seq, const int *token_pos, const void *table,
+                                   const void *positions, int table_dtype, float *x, float *keep, int n_tokens, int d,
+                                   int vocab, int n_positions, int s, int *status, void *stream) {
+    if (n_tokens <= 0) return 0;
+    EmbedPositions p;
+    p.tokens = tokens, p.token_seq = token_seq, p.token_pos = token_pos, p.table = table, p.positions = positions;
+    p.x = x, p.keep = keep, p.d = d, p.vocab = vocab, p.n_positions = n_positions, p.s = s, p.status = status;
+    const int threads = d >= 1024 ? 256 : 128;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (table_dtype == ABK_BF16)
+        abk_launch(embed_positions_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, st, p);
+    else
+        abk_launch(embed_positions_kernel<float>, dim3(n_tokens), dim3(threads), 0, st, p);
+    return ABK_LAUNCH_RESULT();
+}
+
+// x[t, a] += kept[t] for every stream a (x float32 [tokens, s, d], kept float32 [tokens, d]).
+__global__ void __launch_bounds__(256) rejoin_kernel(float *x, const float *kept, long long total, int s, int d) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / ((long long)s * d);
+    x[i] += kept[t * d + i % d];
+}
+
+extern "C" int abk_rejoin(float *x, const float *kept, int n_tokens, int s, int d, void *stream) {
+    const long long total = (long long)n_tokens * s * d;
+    if (total <= 0) return 0;
+    abk_launch(rejoin_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, kept, total, s, d);
+    return ABK_LAUNCH_RESULT();
+}
+
+// out[t] = share * (wa * a[t] / rms(a[t]) + wb * b[t] / rms(b[t])): two branches that ran side by side, each normed over
+// the width with a weight of its own, then joined. All float32; a block a row.
+__global__ void __launch_bounds__(128) normed_pair_kernel(const float *a, const float *b, const float *wa, const float *wb,
+                                                          float *out, int d, float eps, float share) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const float *ar = a + t * d, *br = b + t * d;
+    float sa = 0.0f, sb = 0.0f;
+    for (int j = threadIdx.x; j < d; j += 128) sa = fmaf(ar[j], ar[j], sa), sb = fmaf(br[j], br[j], sb);
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ra = 1.0f / sqrtf(sa / (float)d + eps), rb = 1.0f / sqrtf(sb / (float)d + eps);
+    for (int j = threadIdx.x; j < d; j += 128) out[t * d + j] = share * (ar[j] * ra * wa[j] + br[j] * rb * wb[j]);
+}
+
+extern "C" int abk_normed_pair(const float *a, const float *b, const float *wa, const float *wb, float *out, int n_tokens,
+                               int d, float eps, float share, void *stream) {
+    if (n_tokens <= 0 || d <= 0) return 0;
+    abk_launch(normed_pair_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, a, b, wa, wb, out, d, eps, share);
+    return ABK_LAUNCH_RESULT();
+}

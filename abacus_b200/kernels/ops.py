@@ -165,7 +165,7 @@ def advance_decode(batch):
 
 
 def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, v_dim=None,
-                      keep_first=0, sink=None, exact_weights=False, row=None):
+                      keep_first=0, sink=None, exact_weights=False, row=None, chunk=None, softcap=None):
     """Causal grouped-query attention of every token of the step (src/model.c:197-211).
 
     q is read from qkv's q columns. Keys and values come from `cache` (a cache.LayerView), or, with
@@ -173,7 +173,8 @@ def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ba
     v_dim: the size of a value head (default head_dim). keep_first (with a window): the sequence's first keys
     stay visible. sink: float32 [n_heads], a score per head that joins the denominator. exact_weights: the
     softmax's weights stay float32 in the second product. row: elements between rows of qkv where a row has padding
-    behind its heads.
+    behind its heads. chunk: a token sees only the keys of its own run of `chunk` positions (counted from the
+    sequence's first). softcap: scores become softcap * tanh(score / softcap) after the scale.
     """
     _need_cuda(qkv, out, sink)
     lib = load_module("attention_generic")
@@ -189,14 +190,14 @@ def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, ba
     v_step = ctypes.c_void_p(qkv.data_ptr() + (n_heads + n_kv_heads) * head_dim * esize) if from_step else ctypes.c_void_p(0)
     if not from_step:
         assert cache is not None and cache.k.dtype == qkv.dtype and cache.v.shape[-1] == vd
-    _check(lib, lib.abk_attention_general(
+    _check(lib, lib.abk_attention_chunked(
         _p(qkv), _ll(row), _p(out), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale),
         _i(window or 0), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start),
         _p(batch.seq_pos0), _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
         _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
         _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
         k_step, v_step, _ll(row), _i(vd), _i(keep_first or 0), _i(cache.pinned_pages if cache is not None else 0),
-        _p(sink), _i(1 if exact_weights else 0), _stream()), "attention")
+        _p(sink), _i(1 if exact_weights else 0), _i(chunk or 0), _f(softcap or 0.0), _stream()), "attention")
 
 
 def gemm_simt(x, w, out, m=None):
@@ -354,13 +355,19 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
 
 
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None,
-              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False, row=None):
+              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False, row=None, chunk=None, softcap=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
     (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel.
     prepare: see attention_decode (only where attention_decode_prepares() said yes for this step).
     v_dim, keep_first, sink, exact_weights: see attention_generic and attention_window; the kernels for plain heads
     take none of them."""
+    if chunk or softcap:  # the general kernel alone knows chunks and capped scores
+        assert prepare is None, "q, k and v must be prepared before this kernel"
+        attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step,
+                          v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights, row=row, chunk=chunk,
+                          softcap=softcap)
+        return
     if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights or row:
         assert prepare is None, "q, k and v must be prepared before these kernels"
         if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
@@ -771,9 +778,46 @@ def remember_tokens(batch, remembered):
                                         _p(remembered), _stream()), "remember_tokens")
 
 
+def embed_positions(batch, table, positions, x, keep, status):
+    """x[t, a] = table[token] + positions[position] for every stream a (x float32 [tokens, s, d]): an embedding with a
+    learned vector per position, not scaled. keep (float32 [tokens, d] or None) gets a copy of what the embedding leaves.
+    A token or a position outside its table sets bit 0 of status and gives zeros."""
+    _need_cuda(table, positions, x, keep, status)
+    lib = load_module("streams")
+    n, s, d = batch.n_rows, x.shape[1], x.shape[2]
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape[0] >= n and table.is_contiguous() and table.shape[1] == d
+    assert positions.dtype == table.dtype and positions.is_contiguous() and positions.shape[1] == d
+    assert keep is None or (keep.dtype == torch.float32 and keep.is_contiguous() and keep.shape[0] >= n and keep.shape[1] == d)
+    _check(lib, lib.abk_embed_positions(_p(batch.tokens), _p(batch.token_seq), _p(batch.token_pos), _p(table), _p(positions),
+                                        _i(_dt(table)), _p(x), _p(keep), _i(n), _i(d), _i(table.shape[0]),
+                                        _i(positions.shape[0]), _i(s), _p(status), _stream()), "embed_positions")
+
+
+def rejoin(x, kept, n):
+    """x[t, a] += kept[t] for every stream a and t < n (x float32 [tokens, s, d], kept float32 [tokens, d])."""
+    _need_cuda(x, kept)
+    lib = load_module("streams")
+    assert x.dtype == kept.dtype == torch.float32 and x.is_contiguous() and kept.is_contiguous()
+    assert x.shape[0] >= n and kept.shape[0] >= n and x.shape[2] == kept.shape[1]
+    _check(lib, lib.abk_rejoin(_p(x), _p(kept), _i(n), _i(x.shape[1]), _i(x.shape[2]), _stream()), "rejoin")
+
+
+def normed_pair(a, b, weight_a, weight_b, out, n, eps, share):
+    """out[t] = share * (weight_a * a[t] / rms(a[t]) + weight_b * b[t] / rms(b[t])), rms(v) = sqrt(mean(v^2) + eps): two
+    branches that ran side by side, each normed over the width with a plain weight of its own. All float32 [tokens, d]."""
+    _need_cuda(a, b, weight_a, weight_b, out)
+    lib = load_module("streams")
+    d = out.shape[1]
+    for t in (a, b, out):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == d and t.shape[0] >= n
+    assert weight_a.dtype == weight_b.dtype == torch.float32 and weight_a.numel() == weight_b.numel() == d
+    _check(lib, lib.abk_normed_pair(_p(a), _p(b), _p(weight_a), _p(weight_b), _p(out), _i(n), _i(d), _f(eps), _f(share),
+                                    _stream()), "normed_pair")
+
+
 # ------------------------------------------------------------------ the delta-rule mixer (csrc/delta_rule.cu)
-def short_conv(x, channels, weight, tail, out, batch, update_tail=False):
-    """out[t, c] = silu(sum_j weight[c, j] * x[position - (taps - 1 - j), c]) over the first `channels` columns of x
+def short_conv(x, channels, weight, tail, out, batch, update_tail=False, plain=False):
+    """out[t, c] = silu(sum_j weight[c, j] * x[position - (taps - 1 - j), c]) (plain: the sum without the SiLU) over the first `channels` columns of x
     (rows of any pitch), per sequence: zeros before its start, the slot's tail (float32 [slots, taps - 1, channels])
     before this step's rows. update_tail (only where every sequence of the step brings one token): the kernel leaves
     the slots' new tails itself, and short_conv_tail is not needed."""
@@ -786,7 +830,7 @@ def short_conv(x, channels, weight, tail, out, batch, update_tail=False):
     assert tail.dtype == torch.float32 and tail.shape[1:] == (max(taps - 1, 0), channels) and tail.is_contiguous()
     _check(lib, lib.abk_short_conv(_p(x), _ll(x.stride(0)), _p(out), _i(_dt(x)), _p(weight), _p(tail), _p(batch.token_seq),
                                    _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_pos0), _i(n), _i(channels),
-                                   _i(taps), _i(1 if update_tail else 0), _stream()), "short_conv")
+                                   _i(taps), _i(1 if update_tail else 0), _i(1 if plain else 0), _stream()), "short_conv")
 
 
 def short_conv_tail(x, channels, taps, tail, batch):
@@ -801,41 +845,50 @@ def short_conv_tail(x, channels, taps, tail, batch):
                                         _stream()), "short_conv_tail")
 
 
-def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim, ws):
+def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim, ws,
+               per_head=False):
     """The gated delta rule over every sequence of the step, token by token, from and into the slots' states (float32
     [slots, heads, value, key]). qkv [tokens, 2 * kv_heads * key + heads * value]: q, k and v after their convolution;
     decay_in float32 [tokens, heads * key] (rows of any pitch) before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
-    before the sigmoid; out float32 [tokens, heads * value], not yet normed. Two kernels: every (token, head) is
+    before the sigmoid; out float32 [tokens, heads * value], not yet normed. per_head: one decay for all key channels of a
+    head; decay_in is then [tokens, >= heads] of qkv's type and dt_bias [heads]. Two kernels: every (token, head) is
     prepared in parallel into scratch memory from ws (a parts.Workspace), then the sequences are walked."""
     _need_cuda(qkv, decay_in, beta_in, a_log, dt_bias, state, out)
     lib = load_module("delta_rule")
     lib.abk_delta_scan_scratch.restype = ctypes.c_longlong
     n, n_seqs = batch.n_rows, batch.seq_slot.numel()
     assert qkv.is_contiguous() and qkv.shape[1] == 2 * n_kv_heads * key_dim + n_heads * value_dim and qkv.shape[0] >= n
-    assert decay_in.dtype == torch.float32 and decay_in.stride(1) == 1 and decay_in.shape[1] == n_heads * key_dim
+    if per_head:
+        assert decay_in.dtype == qkv.dtype and decay_in.stride(1) == 1 and decay_in.shape[1] >= n_heads and dt_bias.numel() == n_heads
+    else:
+        assert decay_in.dtype == torch.float32 and decay_in.stride(1) == 1 and decay_in.shape[1] == n_heads * key_dim
+        assert dt_bias.numel() == n_heads * key_dim
     assert beta_in.dtype == qkv.dtype and beta_in.stride(1) == 1 and beta_in.shape[1] >= n_heads
-    assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and dt_bias.numel() == n_heads * key_dim
+    assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == n_heads
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, value_dim, key_dim)
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == n_heads * value_dim
     records = ws.get("delta_records", (int(lib.abk_delta_scan_scratch(_i(n), _i(n_heads), _i(key_dim), _i(value_dim))),),
                      torch.float32)
-    _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)), _p(beta_in),
-                                   _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq),
+    _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)),
+                                   _i(1 if per_head else 0), _p(beta_in), _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq),
                                    _p(batch.seq_start), _p(batch.seq_slot), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv_heads),
                                    _i(key_dim), _i(value_dim), _p(records), _ll(records.numel()), _stream()),
            "delta_scan", kernels=2)
 
 
-def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps):
-    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]); o and gate float32
-    [tokens, heads * value] (gate: rows of any pitch), weight float32 [value]."""
+def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps, silu=False):
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]) (silu: times gate * sigmoid(gate));
+    o float32 [tokens, heads * value]; gate float32 or of out's type, [tokens, heads * value] (rows of any pitch); weight
+    float32 [value], shared by the heads, or [heads * value]."""
     _need_cuda(o, gate, weight, out)
     lib = load_module("delta_rule")
-    assert o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
-    assert o.is_contiguous() and gate.stride(1) == 1 and out.is_contiguous() and weight.numel() == value_dim
+    assert o.dtype == torch.float32 and gate.dtype in (torch.float32, out.dtype) and weight.dtype == torch.float32
+    assert o.is_contiguous() and gate.stride(1) == 1 and out.is_contiguous() and weight.numel() in (value_dim, n_heads * value_dim)
     assert o.shape[1] == gate.shape[1] == out.shape[1] == n_heads * value_dim
-    _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _ll(gate.stride(0)), _p(weight), _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads),
-                                        _i(value_dim), _f(eps), _stream()), "gated_head_norm")
+    _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _ll(gate.stride(0)), _i(0 if gate.dtype == torch.float32 else 1), _p(weight),
+                                        _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads), _i(value_dim), _f(eps),
+                                        _i(1 if silu else 0), _i(1 if weight.numel() != value_dim else 0), _stream()),
+           "gated_head_norm")
 
 
 # ------------------------------------------------------------------ latent attention (csrc/latent.cu)
@@ -989,16 +1042,54 @@ def gated_row_norm(o, gate, weight, out, eps, batch):
                                        _i(width), _f(eps), _p(batch.token_seq), _stream()), "gated_row_norm")
 
 
+# ------------------------------------------------------------------ a matrix memory with exponential gates (csrc/matrix_memory.cu)
+def matrix_memory_blocks(value_dim):
+    """How many copies of n and m a head's state holds (one per CTA that walks the head)."""
+    return int(load_module("matrix_memory").abk_matrix_memory_blocks(_i(value_dim)))
+
+
+def matrix_memory(proj, q_at, k_at, v_at, gates, bias_i, bias_f, cap, denom_eps, n_heads, key_dim, value_dim, state_c,
+                  state_n, state_m, out, batch):
+    """Per head, token by token over every sequence of the step, from and into the slots' states:
+        i = cap tanh((zi + bi) / cap);  f = logsigmoid(cap tanh((zf + bf) / cap));  m' = max(f + m, i)
+        C' = e^(f + m - m') C + e^(i - m') k v^T;  n' likewise with k alone;  o = C'^T q / (max(|n' . q|, e^-m') + denom_eps)
+    q (times key_dim^-1/2 here), k (heads x key) and v (heads x value) are the columns of proj from q_at, k_at and v_at on;
+    gates float32 [tokens, 2 * heads] (rows of any pitch): zi, then zf. States float32: state_c [slots, heads, value, key],
+    state_n [slots, heads, blocks, key], state_m [slots, heads, blocks] with blocks = matrix_memory_blocks(value_dim).
+    out float32 [tokens, heads * value], not yet normed."""
+    _need_cuda(proj, gates, bias_i, bias_f, state_c, state_n, state_m, out)
+    lib = load_module("matrix_memory")
+    n_seqs = batch.seq_slot.numel()
+    blocks = matrix_memory_blocks(value_dim)
+    assert proj.stride(1) == 1 and proj.shape[0] >= batch.n_rows and out.dtype == torch.float32 and out.is_contiguous()
+    assert out.shape[1] == n_heads * value_dim and gates.dtype == torch.float32 and gates.stride(1) == 1
+    assert gates.shape[1] >= 2 * n_heads and bias_i.dtype == bias_f.dtype == torch.float32
+    assert bias_i.numel() == bias_f.numel() == n_heads
+    for st, shape in ((state_c, (n_heads, value_dim, key_dim)), (state_n, (n_heads, blocks, key_dim)), (state_m, (n_heads, blocks))):
+        assert st.dtype == torch.float32 and st.is_contiguous() and tuple(st.shape[1:]) == shape
+    assert batch.seq_start.numel() >= n_seqs + 1
+    _check(lib, lib.abk_matrix_memory(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(q_at), _i(k_at), _i(v_at), _p(gates),
+                                      _ll(gates.stride(0)), _p(bias_i), _p(bias_f), _f(cap), _f(denom_eps),
+                                      _f(float(key_dim) ** -0.5), _i(n_heads), _i(key_dim), _i(value_dim), _p(state_c),
+                                      _p(state_n), _p(state_m), _p(out), _p(batch.seq_start), _p(batch.seq_slot), _i(n_seqs),
+                                      _stream()), "matrix_memory")
+
+
 # ------------------------------------------------------------------ routed experts (csrc/moe.cu)
 RELU_SQUARED = 1
+SILU_GATED = 2  # the matrix holds gate rows, then up rows: silu(gate . x) * (up . x)
 
 
-def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=False, always=None):
+def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=False, always=None, softmax_all=False,
+              correction=None, weight_scale=1.0, n_real=None):
     """Per token the `top` experts with the largest router logits (router float32 [experts, d], x as stored) and their
     weights, sigmoid(logit) or the softmax over the chosen; pair token * top + k is the token's k-th choice
     (pair_expert int32, -1 for padding rows; pair_weight float32). always (an expert's index): every token has top + 1
-    pairs, the last that expert with weight 1."""
-    _need_cuda(x, router, pair_expert, pair_weight)
+    pairs, the last that expert with weight 1. softmax_all: s = softmax over all router outputs, the choice goes by
+    s + correction (float32 [outputs] or None), the weight is s * weight_scale. n_real: router outputs from there on stand
+    for experts that return their input; such a pair carries -2 - (output - n_real)."""
+    _need_cuda(x, router, pair_expert, pair_weight, correction)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == router.shape[0])
     lib = load_module("moe")
     n, (experts, d) = batch.n_rows, router.shape
     assert router.dtype == torch.float32 and router.is_contiguous() and x.stride(1) == 1 and x.shape[1] == d
@@ -1006,17 +1097,22 @@ def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=Fa
     per = top + (0 if always is None else 1)
     assert pair_expert.numel() >= n * per and pair_weight.numel() >= n * per
     _check(lib, lib.abk_moe_route(_p(x), _ll(x.stride(0)), _i(_dt(x)), _p(router), _i(n), _i(d), _i(experts), _i(top),
-                                  _i(1 if softmax_chosen else 0), _i(-1 if always is None else always), _p(batch.token_seq),
-                                  _p(pair_expert), _p(pair_weight), _stream()), "moe_route")
+                                  _i(2 if softmax_all else 1 if softmax_chosen else 0), _i(-1 if always is None else always),
+                                  _p(batch.token_seq), _p(pair_expert), _p(pair_weight), _p(correction), _f(weight_scale),
+                                  _i(experts if n_real is None else n_real), _stream()), "moe_route")
 
 
 def routed_product(x, pairs_per_row, w, pair_expert, pair_scale, out, n_pairs, activation=0):
     """out[p] = act(w[pair_expert[p]] (pair_scale[p] * x[p // pairs_per_row])) for p < n_pairs: a product whose matrix,
     w [experts, outs, in], is chosen per row. pair_scale None: no scale; with one the scaled input is rounded to x's
-    type first. out of x's type or float32. activation: 0 none, RELU_SQUARED."""
+    type first. out of x's type or float32. activation: 0 none, RELU_SQUARED, or SILU_GATED (w [experts, 2 * outs, in]: gate
+    rows, then up rows). Pairs whose expert is negative give zeros."""
     _need_cuda(x, w, pair_expert, pair_scale, out)
     lib = load_module("moe")
     experts, outs, inner = w.shape
+    if activation == SILU_GATED:
+        assert outs % 2 == 0
+        outs //= 2
     assert x.dtype == w.dtype and w.is_contiguous() and x.stride(1) == 1 and x.shape[1] == inner
     assert out.stride(1) == 1 and out.shape[1] == outs and out.shape[0] >= n_pairs and out.dtype in (x.dtype, torch.float32)
     _check(lib, lib.abk_routed_product(_p(x), _ll(x.stride(0)), _i(pairs_per_row), _i(_dt(x)), _p(w), _p(pair_expert),
@@ -1033,6 +1129,19 @@ def moe_combine(pairs, out, n, top, add):
     assert pairs.dtype == out.dtype == torch.float32 and pairs.is_contiguous() and out.is_contiguous()
     assert pairs.shape[1] == d and pairs.shape[0] >= n * top and out.shape[0] >= n
     _check(lib, lib.abk_moe_combine(_p(pairs), _p(out), _i(n), _i(d), _i(top), _i(1 if add else 0), _stream()), "moe_combine")
+
+
+def moe_combine_weighted(pairs, weight, expert, x, out, n, top):
+    """out[t] = sum over k of weight[t * top + k] * (pairs[t * top + k], or x[t] where expert[t * top + k] <= -2: an expert
+    that returns its input), in the order of k; pairs, weight and out float32, x as stored."""
+    _need_cuda(pairs, weight, expert, x, out)
+    lib = load_module("moe")
+    d = out.shape[1]
+    assert pairs.dtype == out.dtype == weight.dtype == torch.float32 and pairs.is_contiguous() and out.is_contiguous()
+    assert pairs.shape[1] == d and pairs.shape[0] >= n * top and out.shape[0] >= n and x.stride(1) == 1 and x.shape[1] == d
+    assert expert.dtype == torch.int32
+    _check(lib, lib.abk_moe_combine_weighted(_p(pairs), _p(weight), _p(expert), _p(x), _ll(x.stride(0)), _i(_dt(x)), _p(out),
+                                             _i(n), _i(d), _i(top), _stream()), "moe_combine_weighted")
 
 
 def relu_squared(x, n):

@@ -1,4 +1,4 @@
-from . import movarax, qwen3, temetar  # noqa: F401  (register Qwen3ForCausalLM, Temetar and Movarax)
+from . import linonex, movarax, qwen3, temetar  # noqa: F401  (register Qwen3ForCausalLM, Temetar, Movarax and Linonex)
 from .layout import ModelLayout
 from .model import Model, expected_tensors
 

@@ -57,6 +57,8 @@ class Model:
             if e.source is not None and not (0 <= e.source < i and self.schedule[e.source].source is None):
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.source}, "
                                  "which must be an earlier entry with a cache of its own")
+            if e.rejoin and not hasattr(self.frame, "rejoin"):
+                raise ValueError(f"schedule entry {i} joins the embedding again, which the frame {spec.frame!r} cannot do")
         self.ws = Workspace(self.ctx.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.ctx.device)
 
@@ -113,5 +115,7 @@ class Model:
             x = self.frame.embed(batch, ws, self.status)
         y = None
         for i, entry in enumerate(self.schedule):
+            if entry.rejoin:  # the embedding joins the stream again (the branch still pending is added after it)
+                self.frame.rejoin(x, batch)
             y = self.blocks[entry.layer].forward(x, y, batch, cache.views[i], ws)
         return self.frame.logits(x, y, batch, ws)

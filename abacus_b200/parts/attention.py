@@ -3,6 +3,11 @@
 The mixer owns the q/k/v and output projections, the optional per-head norm of
 q and k, and a position encoding; its sizes, scale, eps and window come from
 its spec. q, k and v are one stacked matrix, as in src/model.c:88-93.
+
+Options of the spec that only the general kernels take: values of another size than keys, a sequence's first keys
+kept behind a window, a sink, float32 weights, a short causal convolution over time on every channel of q, k and v
+right after their projection (its last inputs are part of the sequence's state, beside the keys and values), keys
+seen only within the token's own chunk of positions, and capped scores.
 """
 import os
 
@@ -37,7 +42,14 @@ class Attention:
         if s.keep_first and s.window is None:
             raise ValueError("keep_first goes with a window")
         # what only the general kernel takes: values of another size, kept first keys, a sink, float32 weights
-        self.general = self.v_dim != s.head_dim or bool(s.keep_first) or s.sink or s.exact_weights
+        self.general = (self.v_dim != s.head_dim or bool(s.keep_first) or s.sink or s.exact_weights or s.conv_taps > 0
+                        or bool(s.chunk) or bool(s.softcap))
+        if s.conv_taps < 0 or s.conv_taps > 8:
+            raise ValueError(f"conv_taps {s.conv_taps}: the convolution takes 1 to 8 taps")
+        if s.chunk is not None and s.chunk < 1:
+            raise ValueError(f"chunk {s.chunk}: a chunk has at least one position")
+        if s.softcap is not None and not s.softcap > 0:
+            raise ValueError(f"softcap {s.softcap}: the cap of the scores is positive")
         if s.head_dim > 256 or s.head_dim < 1 or (s.head_dim % 8 and not self.general):
             raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples of 8 up to 256 (the general "
                              "kernel, which a layer with a sink, kept first keys or values of their own size runs on, "
@@ -62,7 +74,7 @@ class Attention:
 
     def step_weights(self):
         """The tensors a step reads once whatever its size (for the bytes a decode step must move)."""
-        return [self.qkv_proj.weight, self.o_proj.weight, self.q_norm, self.k_norm, self.sink]
+        return [self.qkv_proj.weight, self.o_proj.weight, self.q_norm, self.k_norm, self.sink, self.conv]
 
     def param_shapes(self):
         s = self.spec
@@ -72,6 +84,9 @@ class Attention:
             shapes.update(q_norm=(s.head_dim,), k_norm=(s.head_dim,))
         if s.sink:
             shapes["sink"] = (s.n_heads,)
+        if s.conv_taps:
+            shapes.update(conv_q=(self.q_size, s.conv_taps), conv_k=(self.kv_size, s.conv_taps),
+                          conv_v=(self.v_size, s.conv_taps))
         return shapes
 
     def bind(self, params, ctx):
@@ -85,11 +100,18 @@ class Attention:
         self.q_norm = to_device(params["q_norm"], ctx, torch.float32) if "q_norm" in params else None
         self.k_norm = to_device(params["k_norm"], ctx, torch.float32) if "k_norm" in params else None
         self.sink = to_device(params["sink"], ctx, torch.float32) if "sink" in params else None
+        self.conv = None
+        if self.spec.conv_taps:  # one table for the whole row of q, k and v; the row's padding has taps of zero
+            taps = torch.cat([params["conv_q"], params["conv_k"], params["conv_v"]], dim=0).to(torch.float32)
+            table = torch.zeros((self.row, self.spec.conv_taps), dtype=torch.float32)
+            table[:taps.shape[0]] = taps
+            self.conv = to_device(table, ctx, torch.float32)
 
     def cache_need(self):
         s = self.spec
+        states = (("conv_tail", (s.conv_taps - 1, self.row), "float32"),) if s.conv_taps > 1 else ()
         return CacheNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window, v_head_dim=self.v_dim,
-                         keep_first=s.keep_first if s.window is not None else 0)
+                         keep_first=s.keep_first if s.window is not None else 0, states=states)
 
     def prepare(self, max_positions, device):
         if self.position is not None:
@@ -115,8 +137,19 @@ class Attention:
             ops.gemm_tc_qkv(xn, w, qkv, s.n_heads, s.n_kv_heads, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
                             self.cos, self.sin, cache.kv, n)
             prepared = True
+        elif writes and self.conv is not None:
+            # the projection, then the convolution over time into the row the kernels read; the slot's tail follows
+            proj = ws.get("qkv_proj", (n, self.row), self.ctx.dtype)
+            self.qkv_proj.forward(xn, proj, n)
+            tail = cache.states["conv_tail"] if s.conv_taps > 1 else ws.get("no_tail", (1, 0, self.row), torch.float32)
+            ops.short_conv(proj, self.row, self.conv, tail, qkv, batch, update_tail=batch.is_decode, plain=True)
+            if s.conv_taps > 1 and not batch.is_decode:
+                ops.short_conv_tail(proj, self.row, s.conv_taps, tail, batch)
         elif writes:
             self.qkv_proj.forward(xn, qkv, n)
+        elif self.conv is not None:
+            raise ops.KernelRefused("an attention entry with a convolution keeps a state of its own; it cannot read "
+                                    "another entry's cache")
         else:  # keys and values are another entry's: only q is needed
             self.q_proj.forward(xn, qkv[:, :self.q_size], n)
         prepare = None
@@ -137,6 +170,6 @@ class Attention:
         ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
                       from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare,
                       v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights,
-                      row=self.row if self.general else None)
+                      row=self.row if self.general else None, chunk=s.chunk, softcap=s.softcap)
         self.o_proj.forward(att, out, n)
         return out

@@ -117,3 +117,60 @@ class PairsFrame:
             read_streams(x, pending, self.ones, self.final_norm, xn, rows=batch.logit_rows, n_rows=r)
             self.head.forward(xn, out, r)
         return out
+
+
+@FRAMES.register("positions")
+class PositionsFrame:
+    """x = table[token] + positions[position]: a learned vector per position, added unscaled (config.specs.
+    PositionEmbeddingSpec). The stream is [rows, 1, hidden] (parts/streams.py). With `keep` the frame holds on to x as
+    the embedding left it, and rejoin() adds it to the stream again where the schedule says so (a run of layers that
+    is gone through more than once). The end is the plain frame's: the pending branch, the last norm, the output
+    matrix on the wanted rows."""
+    capturable = True  # launches kernels only
+
+    def __init__(self, spec):
+        self.hidden, self.vocab = spec.hidden, spec.vocab
+        self.options = spec.frame_spec
+        self.final_norm = NORMS.build(spec.final_norm)
+
+    def param_shapes(self, tied):
+        shapes = {"embed": (self.vocab, self.hidden), "positions": (self.options.max_positions, self.hidden),
+                  "final_norm": tuple(self.final_norm.param_shapes()["weight"])}
+        if not tied:
+            shapes["head"] = (self.vocab, self.hidden)
+        return shapes
+
+    def bind(self, params, ctx):
+        self.ctx = ctx
+        self.table = to_device(params["embed"], ctx, ctx.dtype)
+        self.positions = to_device(params["positions"], ctx, ctx.dtype)
+        self.tied = "head" not in params
+        self.head = Linear(self.table if self.tied else to_device(params["head"], ctx, ctx.dtype))
+        self.final_norm.bind({"weight": params["final_norm"]}, ctx)
+        self.ones = torch.ones(1, dtype=torch.float32, device=ctx.device)
+        self.kept = None
+
+    def step_weights(self):
+        return [self.head.weight, *self.final_norm.step_weights()]
+
+    def embed(self, batch, ws, status):
+        x = ws.get("x_streams", (batch.n_rows, 1, self.hidden), torch.float32)
+        self.kept = ws.get("x_embedded", (batch.n_rows, self.hidden), torch.float32) if self.options.keep else None
+        ops.embed_positions(batch, self.table, self.positions, x, self.kept, status)
+        return x
+
+    def rejoin(self, x, batch):
+        """x += what the embedding left, for every row of the step."""
+        if self.kept is None:
+            raise ValueError("the schedule joins the embedding again, but the frame does not keep it")
+        ops.rejoin(x, self.kept, batch.n_rows)
+
+    def logits(self, x, pending, batch, ws):
+        from .streams import read_streams
+        r = batch.n_logit_rows
+        out = ws.get("logits", (max(r, 1), self.vocab), torch.float32)[:r]
+        if r:
+            xn = ws.get("xn_final", (r, self.hidden), self.ctx.dtype)
+            read_streams(x, pending, self.ones, self.final_norm, xn, rows=batch.logit_rows, n_rows=r)
+            self.head.forward(xn, out, r)
+        return out

@@ -14,7 +14,7 @@ from ..kernels import ops
 from .base import FEED_FORWARDS, to_device
 from .linear import Linear
 
-_ACTIVATIONS = {"relu_squared": ops.RELU_SQUARED}
+_ACTIVATIONS = {"relu_squared": ops.RELU_SQUARED, "silu_gated": ops.SILU_GATED}
 # Up to which size of an expert's matrix a shared expert of the same size lies stacked behind the routed ones: small
 # experts are bound by their launches, and the shared one then costs none of its own (width 1,024, experts of 768:
 # 1.94 -> 1.76 ms a decode step of 8 rows); large ones by their bytes, and a product by expert reads the shared matrices
@@ -31,20 +31,37 @@ class RoutedMLP:
 
     def __init__(self, spec):
         s = self.spec = spec
-        if not 1 <= s.top <= s.experts:
-            raise ValueError(f"top {s.top} of {s.experts} experts")
-        if s.score not in ("sigmoid", "softmax_chosen"):
-            raise ValueError(f"router score {s.score!r} is neither sigmoid nor softmax_chosen")
+        if not 1 <= s.top <= s.experts + s.identity:
+            raise ValueError(f"top {s.top} of {s.experts + s.identity} experts")
+        if s.score not in ("sigmoid", "softmax_chosen", "softmax_all"):
+            raise ValueError(f"router score {s.score!r} is none of sigmoid, softmax_chosen, softmax_all")
+        if s.identity < 0 or (s.identity and s.weight_on != "output"):
+            raise ValueError("experts that return their input go with the weight on the experts' outputs")
+        if (s.correction or s.weight_scale != 1.0) and s.score != "softmax_all":
+            raise ValueError("a correction of the choice and a scale of the weights go with the score softmax_all")
+        if s.top > s.experts + s.identity:
+            raise ValueError(f"top {s.top} of {s.experts + s.identity} router outputs")
+        # the weight applied in float32 where a token's pairs are summed (else on the row that enters the last product)
+        self.weighted_sum = s.weight_on == "output" and (s.identity > 0 or s.score == "softmax_all")
+        if self.weighted_sum and s.shared is not None:
+            raise ValueError("a shared expert beside weights on the outputs is not built")
+        self.gated = s.expert.activation == "silu_gated"
         if s.weight_on not in ("input", "output"):
             raise ValueError(f"weight_on {s.weight_on!r} is neither input nor output")
         for e in (s.expert, s.shared):
             if e is not None and e.activation not in _ACTIVATIONS:
-                raise ValueError(f"expert activation {e.activation!r} is not built (only relu_squared)")
+                raise ValueError(f"expert activation {e.activation!r} is not built (relu_squared, silu_gated)")
+        if s.shared is not None and s.shared.activation != "relu_squared":
+            raise ValueError("a shared expert is built with relu_squared only")
 
     def param_shapes(self):
         s = self.spec
-        shapes = {"router": (s.experts, s.hidden)}
+        shapes = {"router": (s.experts + s.identity, s.hidden)}
+        if s.correction:
+            shapes["correction"] = (s.experts + s.identity,)
         for e in range(s.experts):
+            if self.gated:
+                shapes[f"gate{e}"] = (s.expert.inter, s.hidden)
             shapes[f"up{e}"] = (s.expert.inter, s.hidden)
             shapes[f"down{e}"] = (s.hidden, s.expert.inter)
         if s.shared is not None:
@@ -54,7 +71,10 @@ class RoutedMLP:
     def bind(self, params, ctx):
         s, self.ctx = self.spec, ctx
         self.router = to_device(params["router"], ctx, torch.float32)
+        self.correction = to_device(params["correction"], ctx, torch.float32) if s.correction else None
         ups, downs = [params[f"up{e}"] for e in range(s.experts)], [params[f"down{e}"] for e in range(s.experts)]
+        if self.gated:  # an expert's first matrix: its gate rows, then its up rows
+            ups = [torch.cat([params[f"gate{e}"], up], dim=0) for e, up in enumerate(ups)]
         # a shared expert of the routed experts' own size and activation lies stacked behind them, and every token has
         # one more pair: that expert, with weight 1 (no launches of its own; in a prompt it rides the grouped product)
         self.stacked_shared = (s.shared is not None and s.shared.inter == s.expert.inter
@@ -74,7 +94,7 @@ class RoutedMLP:
         if self.stacked_shared:
             return [self.router, self.up[self.spec.experts], self.down[self.spec.experts]]
         shared = [self.shared_up.weight, self.shared_down.weight] if self.shared_up is not None else []
-        return [self.router, *shared]
+        return [self.router, self.correction, *shared]
 
     def forward(self, xn, out, batch, ws):
         s, n, dt = self.spec, batch.n_rows, self.ctx.dtype
@@ -84,8 +104,11 @@ class RoutedMLP:
         expert = ws.get("moe_expert", (pairs,), torch.int32)
         weight = ws.get("moe_weight", (pairs,), torch.float32)
         ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen",
-                      always=s.experts if self.stacked_shared else None)
+                      always=s.experts if self.stacked_shared else None, softmax_all=s.score == "softmax_all",
+                      correction=self.correction, weight_scale=s.weight_scale, n_real=s.experts)
         on_input = s.weight_on == "input"
+        if self.weighted_sum:
+            return self.forward_weighted_sum(xn, out, expert, weight, n, pairs, ws)
         if self.shared_up is not None:
             shared_act = ws.get("moe_shared_act", (n, s.shared.inter), dt)
             self.shared_up.forward(xn, shared_act, n)
@@ -111,4 +134,15 @@ class RoutedMLP:
         pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
         ops.routed_product(act, 1, self.down, expert, None if on_input else weight, pair_out, pairs)
         ops.moe_combine(pair_out, out, n, top, add=self.shared_up is not None)
+        return out
+
+    def forward_weighted_sum(self, xn, out, expert, weight, n, pairs, ws):
+        """The experts' outputs, unweighted, then out[t] = sum_k weight[t, k] * (output of the k-th choice, or the token's
+        own row where the choice returns its input), in float32."""
+        s, dt = self.spec, self.ctx.dtype
+        act = ws.get("moe_act", (pairs, s.expert.inter), dt)
+        ops.routed_product(xn, s.top, self.up, expert, None, act, pairs, activation=_ACTIVATIONS[s.expert.activation])
+        pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
+        ops.routed_product(act, 1, self.down, expert, None, pair_out, pairs)
+        ops.moe_combine_weighted(pair_out, weight, expert, xn, out, n, s.top)
         return out
