@@ -116,12 +116,16 @@ def matrix_memory(h, p, m, eps, state):
 def chunked_attention(h, p, m, state):
     """The left side of "parallel". state: (conv tails of q, k, v; keys; values; tokens seen)."""
     H, G, K, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, cap, scale = m["mask"]["size"], m["softcap"], m["scale"]
+    size = m["mask"]["size"] if m.get("mask") else None   # no mask: every earlier key is seen
+    cap, scale = m.get("softcap"), m["scale"]               # no cap: scores as they are
     T = h.shape[0]
     tails, keys, values, seen = state if state is not None else ((None, None, None), None, None, 0)
-    q, tq = causal_conv(h @ p["q"].T, p["q.conv"], tails[0])
-    k, tk = causal_conv(h @ p["k"].T, p["k.conv"], tails[1])
-    v, tv = causal_conv(h @ p["v"].T, p["v.conv"], tails[2])
+    q, k, v = h @ p["q"].T, h @ p["k"].T, h @ p["v"].T
+    tq = tk = tv = None
+    if "q.conv" in p:                                       # no taps: the projections as they are
+        q, tq = causal_conv(q, p["q.conv"], tails[0])
+        k, tk = causal_conv(k, p["k.conv"], tails[1])
+        v, tv = causal_conv(v, p["v.conv"], tails[2])
     k, v = k.reshape(T, G, K), v.reshape(T, G, V)
     keys = k if keys is None else np.concatenate([keys, k], axis=0)
     values = v if values is None else np.concatenate([values, v], axis=0)
@@ -129,11 +133,12 @@ def chunked_attention(h, p, m, state):
     out = np.zeros((T, H, V), h.dtype)
     for t in range(T):
         i = seen + t
-        first = (i // size) * size
+        first = (i // size) * size if size else 0
         for a in range(H):
             g = a // (H // G)
             s = keys[first:i + 1, g] @ q[t, a] * scale
-            s = cap * np.tanh(s / cap)
+            if cap:
+                s = cap * np.tanh(s / cap)
             w = np.exp(s - s.max())
             out[t, a] = (w / w.sum()) @ values[first:i + 1, g]
     return out.reshape(T, H * V) @ p["o"].T, ((tq, tk, tv), keys, values, seen + T)
