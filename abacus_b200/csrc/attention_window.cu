@@ -4,7 +4,9 @@
 // float32 in the second product.
 //
 //   key j is seen from i when j <= i and (window == 0 or i - j < window or j < keep_first)
+//                                    and (chunk == 0 or j / chunk == i / chunk)
 //   p_j = exp(z_j - M) / (exp(sink - M) + sum_j exp(z_j - M)),  z_j = scale * (q . k_j),  out = sum_j p_j v_j
+//   (with a cap c of the scores, z_j = c tanh(scale * (q . k_j) / c))
 //
 // Keys and values are read from the step's own rows (every sequence of the step starts at position 0), so a
 // windowed layer's ring of cache pages is not touched. A CTA has 64 query rows of one head (four warps of 16
@@ -33,7 +35,9 @@ struct AttnWindow {
     int n_heads, n_kv_heads, head_dim, v_dim;
     int k_off, v_off;
     float scale_log2;          // score scale times log2(e)
+    float scale, softcap;      // softcap > 0: z <- softcap * tanh(scale * (q . k) / softcap), in float32, before the softmax
     int window, keep_first;
+    int chunk;                 // > 0: key j is seen from i only if j / chunk == i / chunk (positions from the sequence's start)
     const float *sink;         // [n_heads] or null
     const int *seq_start;      // [n_seqs + 1]
     int n_seqs;
@@ -94,7 +98,8 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
     const __nv_bfloat16 *kg = base + p.k_off + (long long)kvh * D, *vg = base + p.v_off + (long long)kvh * VD;
 
     // tiles of keys: first those with kept first keys that lie before the window's first tile, then the window's
-    const int lo = p.window > 0 && r0 - p.window + 1 > 0 ? r0 - p.window + 1 : 0;  // first key the CTA's first row sees in its window
+    int lo = p.window > 0 && r0 - p.window + 1 > 0 ? r0 - p.window + 1 : 0;  // first key the CTA's first row sees in its window
+    if (p.chunk > 0) lo = max(lo, r0 / p.chunk * p.chunk);  // or in its chunk (later rows' chunks start no earlier)
     const int w_first = lo / AW_KEYS, w_last = r_last / AW_KEYS;
     const int kept_tiles = p.window > 0 ? min((p.keep_first + AW_KEYS - 1) / AW_KEYS, w_first) : 0;
     const int n_tiles = kept_tiles + w_last - w_first + 1;
@@ -111,6 +116,8 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
     float m[2] = {sink2, sink2}, l[2] = {p.sink ? 1.0f : 0.0f, p.sink ? 1.0f : 0.0f};
     const int n_vt = v16 >> 3;  // value column tiles of 8 (an even number)
     const int row_a = r0 + warp * 16 + g, row_b = row_a + 8;  // the two query rows (positions) this thread has a part of
+    const int chunk_a = p.chunk > 0 ? row_a / p.chunk * p.chunk : 0, chunk_b = p.chunk > 0 ? row_b / p.chunk * p.chunk : 0;
+    const float cap_inv = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f, cap_log2 = p.softcap * 1.4426950408889634f;
 
     for (int it = 0; it < n_tiles; it++) {
         const int stage = p.stages == 2 ? it & 1 : 0, key0 = TILE_AT(it) * AW_KEYS;
@@ -153,14 +160,23 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
         // sequence) needs no look at single keys: most tiles of a long window
         const int warp_first = r0 + warp * 16, warp_last = warp_first + 15;
         const bool clear = !kept_tile && key0 + AW_KEYS - 1 <= warp_first && warp_last < n &&
-                           (p.window <= 0 || warp_last - key0 < p.window);
+                           (p.window <= 0 || warp_last - key0 < p.window) &&
+                           (p.chunk <= 0 || key0 >= warp_last / p.chunk * p.chunk);
+        if (p.softcap > 0.0f) {  // capped scores, in float32: z = cap * tanh(scale * (q . k) / cap)
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[t][e] = cap_log2 * tanhf(s[t][e] * p.scale * cap_inv);
+            }
+        }
+        const float to_log2 = p.softcap > 0.0f ? 1.0f : p.scale_log2;
         float top[2] = {-INFINITY, -INFINITY};
         if (clear) {
 #pragma unroll
             for (int t = 0; t < 8; t++) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    s[t][e] *= p.scale_log2;
+                    s[t][e] *= to_log2;
                     top[e >> 1] = fmaxf(top[e >> 1], s[t][e]);
                 }
             }
@@ -173,7 +189,8 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
                     bool seen = j <= i && i < n;
                     if (kept_tile) seen = seen && j < p.keep_first;
                     else if (p.window > 0) seen = seen && (i - j < p.window || j < p.keep_first);
-                    s[t][e] = seen ? s[t][e] * p.scale_log2 : -INFINITY;
+                    if (p.chunk > 0) seen = seen && j >= (e < 2 ? chunk_a : chunk_b);
+                    s[t][e] = seen ? s[t][e] * to_log2 : -INFINITY;
                     top[e >> 1] = fmaxf(top[e >> 1], s[t][e]);
                 }
             }
@@ -254,7 +271,8 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
 // knows the rows; CTAs beyond the real tiles return at once).
 extern "C" int abk_attention_window(const void *qkv, long long row, void *out, int n_heads, int n_kv_heads, int head_dim,
                                     int v_dim, int k_off, int v_off, float scale, int window, int keep_first,
-                                    const float *sink, const int *seq_start, int n_seqs, int max_tiles, void *stream) {
+                                    const float *sink, const int *seq_start, int n_seqs, int max_tiles, int chunk,
+                                    float softcap, void *stream) {
     if (n_seqs <= 0 || max_tiles <= 0) return 0;
     if (head_dim % 8 || head_dim < 8 || head_dim > 256) ABK_REFUSE("attention_window: head_dim %d is not a multiple of 8 up to 256", head_dim);
     if (v_dim % 8 || v_dim < 8 || v_dim > 8 * AW_MAX_VT) ABK_REFUSE("attention_window: value size %d is not a multiple of 8 up to %d", v_dim, 8 * AW_MAX_VT);
@@ -266,6 +284,7 @@ extern "C" int abk_attention_window(const void *qkv, long long row, void *out, i
     p.qkv = (const __nv_bfloat16 *)qkv, p.row = row, p.out = (__nv_bfloat16 *)out, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.head_dim = head_dim, p.v_dim = v_dim, p.k_off = k_off, p.v_off = v_off, p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window > 0 ? window : 0, p.keep_first = keep_first, p.sink = sink, p.seq_start = seq_start, p.n_seqs = n_seqs;
+    p.scale = scale, p.softcap = softcap > 0.0f ? softcap : 0.0f, p.chunk = chunk > 0 ? chunk : 0;
     const int d16 = (head_dim + 15) & ~15, v16 = (v_dim + 15) & ~15;
     static int stages_env = -1;  // ABACUS_WINDOW_STAGES=1|2 pins the number of stages (for comparison)
     if (stages_env < 0) {

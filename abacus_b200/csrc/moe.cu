@@ -16,7 +16,8 @@
 //                   coalesced. Float32 sums in a fixed order.
 //   moe_combine     out[t] (+)= sum over k of pairs[t * top + k], in the order of k.
 //   moe_combine_weighted  out[t] = sum over k of weight[t, k] * (pairs[t * top + k], or x[t] for an expert that returns
-//                   its input), in the order of k: the weight on the experts' outputs, in float32.
+//                   its input), in the order of k: the weight on the experts' outputs, in float32. The pairs' rows lie in
+//                   the pairs' order, or (with `place`) sorted by expert, pair p at row place[p].
 //   routed_product also has the gated form: W holds gate rows then up rows, out = silu(gate . x) * (up . x).
 //   relu_squared    x = max(x, 0)^2 in place.
 #define ABK_DEFINE_ERROR
@@ -228,7 +229,7 @@ extern "C" int abk_moe_combine(const float *pairs, float *out, int n_tokens, int
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_weighted_kernel(const float *pairs, const float *weight, const int *expert,
                                                                    const T *x, long long ldx, float *out, long long total, int d,
-                                                                   int top) {
+                                                                   int top, const int *place) {
     pdl_wait();
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= total) return;
@@ -237,23 +238,25 @@ __global__ void __launch_bounds__(256) moe_combine_weighted_kernel(const float *
     for (int k = 0; k < top; k++) {
         const int e = expert[t * top + k];
         if (e == -1) continue;  // a padding row
-        acc = fmaf(weight[t * top + k], e >= 0 ? pairs[(t * top + k) * d + j] : to_float(x[t * ldx + j]), acc);
+        const long long at = place && e >= 0 ? place[t * top + k] : t * top + k;  // rows sorted by expert: the pair's place
+        acc = fmaf(weight[t * top + k], e >= 0 ? pairs[at * d + j] : to_float(x[t * ldx + j]), acc);
     }
     out[i] = acc;
 }
 
-// out float32 [tokens][d] = sum_k weight[t, k] * (pairs[t * top + k], or x[t] where expert[t, k] <= -2).
+// out float32 [tokens][d] = sum_k weight[t, k] * (pairs[t * top + k], or x[t] where expert[t, k] <= -2). place (or null):
+// pair p's row in `pairs` is place[p] (rows sorted by expert), not p.
 extern "C" int abk_moe_combine_weighted(const float *pairs, const float *weight, const int *expert, const void *x, long long ldx,
-                                        int dtype, float *out, int n_tokens, int d, int top, void *stream) {
+                                        int dtype, float *out, int n_tokens, int d, int top, const int *place, void *stream) {
     const long long total = (long long)n_tokens * d;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == ABK_BF16)
         abk_launch(moe_combine_weighted_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, pairs, weight,
-                   expert, (const __nv_bfloat16 *)x, ldx, out, total, d, top);
+                   expert, (const __nv_bfloat16 *)x, ldx, out, total, d, top, place);
     else
         abk_launch(moe_combine_weighted_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, pairs, weight, expert,
-                   (const float *)x, ldx, out, total, d, top);
+                   (const float *)x, ldx, out, total, d, top, place);
     return ABK_LAUNCH_RESULT();
 }
 

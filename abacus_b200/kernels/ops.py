@@ -362,8 +362,13 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     prepare: see attention_decode (only where attention_decode_prepares() said yes for this step).
     v_dim, keep_first, sink, exact_weights: see attention_generic and attention_window; the kernels for plain heads
     take none of them."""
-    if chunk or softcap:  # the general kernel alone knows chunks and capped scores
+    if chunk or softcap:  # the general kernel knows chunks and capped scores, and the prompt kernel with float32 weights
         assert prepare is None, "q, k and v must be prepared before this kernel"
+        if (exact_weights and not batch.is_decode and not batch.any_continuation
+                and attention_window_takes(qkv, head_dim, v_dim or head_dim, n_heads, n_kv_heads, row)):
+            attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=v_dim,
+                             keep_first=keep_first, sink=sink, row=row, chunk=chunk, softcap=softcap)
+            return
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step,
                           v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights, row=row, chunk=chunk,
                           softcap=softcap)
@@ -404,10 +409,11 @@ def attention_window_takes(qkv, head_dim, v_dim, n_heads, n_kv_heads, row=None):
 
 
 def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=None, keep_first=0, sink=None,
-                     row=None):
+                     row=None, chunk=None, softcap=None):
     """Causal attention of whole prompts (every sequence of the step from its first token) on the warp-level tensor
     cores, keys and values from the step's own rows of qkv: an optional window that also keeps the first keep_first
-    keys, an optional sink (float32 [n_heads]), values of v_dim, softmax weights in float32 (csrc/attention_window.cu)."""
+    keys, an optional sink (float32 [n_heads]), values of v_dim, softmax weights in float32, keys seen only within the
+    token's own chunk of `chunk` positions, scores capped at `softcap` (csrc/attention_window.cu)."""
     _need_cuda(qkv, out, sink)
     lib = load_module("attention_window")
     vd = v_dim or head_dim
@@ -423,7 +429,7 @@ def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
     _check(lib, lib.abk_attention_window(_p(qkv), _ll(row), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(vd),
                                          _i(n_heads * head_dim), _i((n_heads + n_kv_heads) * head_dim), _f(scale),
                                          _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.seq_start), _i(n_seqs),
-                                         _i(max_tiles), _stream()), "attention_window")
+                                         _i(max_tiles), _i(chunk or 0), _f(softcap or 0.0), _stream()), "attention_window")
 
 
 def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=None, keep_first=0,
@@ -1131,17 +1137,24 @@ def moe_combine(pairs, out, n, top, add):
     _check(lib, lib.abk_moe_combine(_p(pairs), _p(out), _i(n), _i(d), _i(top), _i(1 if add else 0), _stream()), "moe_combine")
 
 
-def moe_combine_weighted(pairs, weight, expert, x, out, n, top):
+def moe_combine_weighted(pairs, weight, expert, x, out, n, top, place=None):
     """out[t] = sum over k of weight[t * top + k] * (pairs[t * top + k], or x[t] where expert[t * top + k] <= -2: an expert
-    that returns its input), in the order of k; pairs, weight and out float32, x as stored."""
+    that returns its input), in the order of k; pairs, weight and out float32, x as stored. place int32: the rows of
+    `pairs` lie sorted by expert, pair p's at place[p]."""
     _need_cuda(pairs, weight, expert, x, out)
     lib = load_module("moe")
     d = out.shape[1]
     assert pairs.dtype == out.dtype == weight.dtype == torch.float32 and pairs.is_contiguous() and out.is_contiguous()
-    assert pairs.shape[1] == d and pairs.shape[0] >= n * top and out.shape[0] >= n and x.stride(1) == 1 and x.shape[1] == d
+    assert pairs.shape[1] == d and out.shape[0] >= n and x.stride(1) == 1 and x.shape[1] == d
     assert expert.dtype == torch.int32
+    if place is None:
+        assert pairs.shape[0] >= n * top
+    else:
+        _need_cuda(place)
+        assert place.dtype == torch.int32 and place.numel() >= n * top
     _check(lib, lib.abk_moe_combine_weighted(_p(pairs), _p(weight), _p(expert), _p(x), _ll(x.stride(0)), _i(_dt(x)), _p(out),
-                                             _i(n), _i(d), _i(top), _stream()), "moe_combine_weighted")
+                                             _i(n), _i(d), _i(top), _p(place) if place is not None else ctypes.c_void_p(0),
+                                             _stream()), "moe_combine_weighted")
 
 
 def relu_squared(x, n):

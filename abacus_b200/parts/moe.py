@@ -140,6 +140,27 @@ class RoutedMLP:
         """The experts' outputs, unweighted, then out[t] = sum_k weight[t, k] * (output of the k-th choice, or the token's
         own row where the choice returns its input), in float32."""
         s, dt = self.spec, self.ctx.dtype
+        if pairs > GROUPED_FROM and ops.grouped_takes(xn, self.up, self.down) and s.expert.inter % 8 == 0:
+            # many rows: sorted by expert for the tensor cores (pairs that return their input have no place there); a
+            # gated expert's first product leaves gate and up side by side, as stored tensors, then the activation
+            tiles = ops.grouped_tiles(pairs, s.experts)
+            rows = tiles * ops.GROUPED_ROWS
+            scratch = ws.get("moe_sort", (2 * s.experts + pairs,), torch.int32)
+            place = ws.get("moe_place", (pairs,), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
+            sorted_rows = ws.get("moe_sorted", (rows, s.hidden), dt)
+            ops.moe_sort(xn, s.top, expert, None, pairs, s.experts, scratch, place, tile_expert, sorted_rows)
+            act = ws.get("moe_act", (rows, s.expert.inter), dt)
+            if self.gated:
+                gate_up = ws.get("moe_gate_up", (rows, 2 * s.expert.inter), dt)
+                ops.gemm_grouped(sorted_rows, self.up, gate_up, tile_expert)
+                ops.swiglu(gate_up, act)
+            else:
+                ops.gemm_grouped(sorted_rows, self.up, act, tile_expert, activation=_ACTIVATIONS[s.expert.activation])
+            sorted_out = ws.get("moe_pair_out", (rows, s.hidden), torch.float32)
+            ops.gemm_grouped(act, self.down, sorted_out, tile_expert)
+            ops.moe_combine_weighted(sorted_out, weight, expert, xn, out, n, s.top, place=place)
+            return out
         act = ws.get("moe_act", (pairs, s.expert.inter), dt)
         ops.routed_product(xn, s.top, self.up, expert, None, act, pairs, activation=_ACTIVATIONS[s.expert.activation])
         pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)

@@ -481,17 +481,62 @@ def build_movarax(size):
     return model
 
 
+# Linonex at the same widths, depths and vocabulary: the even layers a matrix memory with exponential gates (heads of
+# 128 x 128 state), the odd layers two mixers side by side: attention over chunks of 1,024 positions (heads of 128, a
+# convolution of 4 taps on q, k and v, scores capped at 30) and the delta rule with a decay per head (heads of 128 x 128
+# state, 4 taps); the first feed-forward dense, the others 16 experts and 2 router outputs that return the input, of
+# which a token uses 2, each expert a quarter of the dense size. No loop: a layer runs once, as in the models beside it.
+LINONEX_SIZES = {
+    "s": dict(heads=16, kv_heads=8, memory_heads=8, delta_heads=8, experts=16, identity=2, top=2, expert_ff=768),
+    "m": dict(heads=32, kv_heads=8, memory_heads=20, delta_heads=20, experts=16, identity=2, top=2, expert_ff=2432),
+}
+
+
+def build_linonex(size):
+    import torch
+    from abacus_b200.config import get_architecture
+    from abacus_b200.config.linonex import (LinonexAttention, LinonexConfig, LinonexDelta, LinonexDense, LinonexExperts,
+                                            LinonexLayer, LinonexMemory, LinonexParallel)
+    from abacus_b200.models import Model
+    from abacus_b200.weights import random_tensors
+    z, v = DESIGN_SIZES[size], LINONEX_SIZES[size]
+    layers = []
+    for i in range(z["layers"]):
+        mlp = LinonexDense(z["ff"]) if i == 0 else LinonexExperts(v["experts"], v["identity"], v["top"], 1.5, v["expert_ff"])
+        if i % 2 == 0:
+            layers.append(LinonexLayer("mlstm", LinonexMemory(v["memory_heads"], 128, 128, 15.0), mlp))
+        else:
+            left = LinonexAttention(v["heads"], v["kv_heads"], 128, 128, 128 ** -0.5, 4, 1024, 30.0)
+            right = LinonexDelta(v["delta_heads"], v["delta_heads"], 128, 128, 4)
+            layers.append(LinonexLayer("parallel", LinonexParallel(left, right), mlp))
+    config = LinonexConfig(vocab=z["vocab"], width=z["width"], layers=tuple(layers), eps=1e-6, max_positions=CONTEXT)
+    arch = get_architecture("Linonex")
+    spec = config.to_spec()
+    expected, _ = arch.tensor_names(spec, None)
+    device = torch.device("cuda", 0)
+    tensors = random_tensors(expected, seed=5, std=0.02, device=device, rule=arch.random_moments)
+    model = Model(spec, arch.layout(spec), tensors, torch.bfloat16, device)
+    del tensors
+    torch.cuda.empty_cache()
+    return model
+
+
 def state_and_cache_bytes(model, tokens_held, n_seqs):
     """Bytes of keys, values and recurrent state a decode step moves for n_seqs sequences that hold tokens_held
-    tokens together: a window's keys at most, a state read and written."""
+    tokens together: a window's keys at most, the keys of the token's own chunk where attention sees no others, a state
+    read and written."""
     total = 0.0
-    for need in model.cache_needs():
+    for e, need in zip(model.schedule, model.cache_needs()):
         if need is None:
             continue
         if need.n_kv_heads:
             per_seq = tokens_held / n_seqs
             if need.window is not None:
                 per_seq = min(per_seq, need.window + need.keep_first)
+            mixer = model.blocks[e.layer].mixer.spec
+            chunk = getattr(getattr(mixer, "left", mixer), "chunk", None)
+            if chunk:
+                per_seq = per_seq % chunk
             values = 0 if need.values_in_keys else (need.v_head_dim or need.head_dim)  # (one pool: read once)
             total += n_seqs * per_seq * need.n_kv_heads * (need.head_dim + values) * 2
         for _, shape, _ in need.states:
@@ -517,8 +562,8 @@ def routed_expert_bytes(model, n_rows):
 
 
 def run_design(args):
-    """--design temetar | movarax: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3 shape of
-    equal size."""
+    """--design temetar | movarax | linonex: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3
+    shape of equal size (--beside: beside another design of equal size instead)."""
     import torch
     from abacus_b200.kernels import build_all
     build_all(verbose=False)
@@ -528,13 +573,17 @@ def run_design(args):
     shape = {k: v for k, v in z.items() if k != "qwen"}
     if args.design == "movarax":
         shape = {**{k: shape[k] for k in ("width", "ff", "layers", "vocab")}, **MOVARAX_SIZES[args.size]}
+    if args.design == "linonex":
+        shape = {**{k: shape[k] for k in ("width", "ff", "layers", "vocab")}, **LINONEX_SIZES[args.size]}
     out = {"design": args.design.capitalize(), "size": args.size, "shape": shape,
            "batch": args.batch, "prompt_tokens": PROMPT, "steps": args.steps, "warmup": args.warmup, "peaks": pk}
-    for which in (args.design, "qwen3"):
+    for which in (args.design, args.beside):
         if which == "temetar":
             model = build_temetar(args.size)
         elif which == "movarax":
             model = build_movarax(args.size)
+        elif which == "linonex":
+            model = build_linonex(args.size)
         else:
             model, _ = build_model(z["qwen"])
         prompts = prompts_for(args.batch, model.spec.vocab, 10 + args.batch)
@@ -643,9 +692,11 @@ def main():
     ap.add_argument("--config", default="0.6b", choices=sorted(CONFIGS), help="whose workload the line reports")
     ap.add_argument("--skip-large", action="store_true", help="leave the 4b and 8b workloads out of `points`")
     ap.add_argument("--ragged", action="store_true", help="with --only prefill: the configuration's own prompts")
-    ap.add_argument("--design", default=None, choices=["temetar", "movarax"],
+    ap.add_argument("--design", default=None, choices=["temetar", "movarax", "linonex"],
                     help="instead of the default workload: this design at --size beside the Qwen3 shape of equal size")
     ap.add_argument("--size", default="s", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
+    ap.add_argument("--beside", default="qwen3", choices=["qwen3", "temetar", "movarax"],
+                    help="with --design: the model of equal size that runs beside it")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not built (no multi-GPU path)")

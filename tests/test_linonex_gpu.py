@@ -234,11 +234,13 @@ def test_attention_with_a_convolution_chunks_and_a_cap_every_way(dtype, H, G, K,
     _every_way(run, h, want, dtype, f"attention {H}/{G}x{K}x{V}, {taps} taps, chunks of {chunk}, cap {cap}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("chunk", [48, 64, 130, 200])
-def test_one_loud_key_at_the_edges_of_chunks_and_pages(chunk):
+def test_one_loud_key_at_the_edges_of_chunks_and_pages(chunk, dtype):
     """Queries read one part of the input row, keys another, values a third, so a key can be made loud for one query
     alone: the first and the last key of the query's chunk, the last key of the chunk before (which must not count), keys
-    on both sides of a page's border, the far end of a long chunk; in a prompt and for tokens that come one by one."""
+    on both sides of a page's border, the far end of a long chunk; in a prompt and for tokens that come one by one. In
+    bfloat16 whole prompts run on the tensor-core kernel, whose tiles of 64 keys have edges of their own."""
     rng, K, V, T = np.random.default_rng(chunk), 8, 8, 210
     d = 2 * K + V
     p = {"q": np.eye(d)[:K], "k": np.eye(d)[K:2 * K], "v": np.eye(d)[2 * K:], "o": np.eye(d)[:, :V],
@@ -253,24 +255,24 @@ def test_one_loud_key_at_the_edges_of_chunks_and_pages(chunk):
         first = i // chunk * chunk
         pairs += [(i, first), (i, i), (i, max(first - 1, 0)), (i, max(i - 1, 0)), (i, min(first + 63, i)), (i, min(first + 64, i))]
     run = PartRun(_attention_spec(d, 1, 1, K, V, 1.0, 2, chunk, 25.0),
-                  _attention_params({n: t.astype(np.float32) for n, t in p.items()}, 2), "float32")
+                  _attention_params({n: t.astype(np.float32) for n, t in p.items()}, 2), dtype)
     for i, j in sorted(set(pairs)):
         h = rng.standard_normal((T, d)) * 0.2
         h[i, :K] = 6.0 * u
         h[j, K:2 * K] = 6.0 * u
-        h = h.astype(np.float32)
+        h = _rnd(dtype)(h)
         want, _ = plain.chunked_attention(h.astype(np.float64), {n: t.astype(np.float64) for n, t in p.items()}, m, None)
         seen = j // chunk == i // chunk and j <= i
         if j != i:  # the loud key decides the answer if and only if it lies in the query's chunk
             assert (np.abs(want[i, :V] - h[j, 2 * K:]).max() < 0.05) == seen
         run.cache.views[0].kv.k.fill_(9.0), run.cache.views[0].kv.v.fill_(9.0)  # what former users left in the pages
         slot = run.open(dirty=True)
-        _close(run.step([(slot, h[:i + 1])])[0], want[:i + 1], "float32", f"query {i}, loud key {j}, prompt")
+        _close(run.step([(slot, h[:i + 1])])[0], want[:i + 1], dtype, f"query {i}, loud key {j}, prompt")
         run.cache.close_slot(slot)
         # the prompt ends a few tokens before the query, or right before the key if that comes later
         slot, cut = run.open(dirty=True), max(1, i - 3 if j < i - 3 else j - 1)
         got = [run.step([(slot, h[:cut])])[0]] + [run.step([(slot, h[t:t + 1])])[0] for t in range(cut, i + 1)]
-        _close(np.concatenate(got), want[:i + 1], "float32", f"query {i}, loud key {j}, decoded from {cut}")
+        _close(np.concatenate(got), want[:i + 1], dtype, f"query {i}, loud key {j}, decoded from {cut}")
         run.cache.close_slot(slot)
 
 
