@@ -1054,15 +1054,20 @@ def matrix_memory_blocks(value_dim):
     return int(load_module("matrix_memory").abk_matrix_memory_blocks(_i(value_dim)))
 
 
+MATRIX_MEMORY_CHUNK = 64  # tokens of a chunk of the chunked form
+
+
 def matrix_memory(proj, q_at, k_at, v_at, gates, bias_i, bias_f, cap, denom_eps, n_heads, key_dim, value_dim, state_c,
-                  state_n, state_m, out, batch):
+                  state_n, state_m, out, batch, ws=None):
     """Per head, token by token over every sequence of the step, from and into the slots' states:
         i = cap tanh((zi + bi) / cap);  f = logsigmoid(cap tanh((zf + bf) / cap));  m' = max(f + m, i)
         C' = e^(f + m - m') C + e^(i - m') k v^T;  n' likewise with k alone;  o = C'^T q / (max(|n' . q|, e^-m') + denom_eps)
     q (times key_dim^-1/2 here), k (heads x key) and v (heads x value) are the columns of proj from q_at, k_at and v_at on;
     gates float32 [tokens, 2 * heads] (rows of any pitch): zi, then zf. States float32: state_c [slots, heads, value, key],
     state_n [slots, heads, blocks, key], state_m [slots, heads, blocks] with blocks = matrix_memory_blocks(value_dim).
-    out float32 [tokens, heads * value], not yet normed."""
+    out float32 [tokens, heads * value], not yet normed. ws (a parts.Workspace): the same recurrence in chunks of 64
+    tokens, for steps that bring prompts: the chunks' sums and outputs side by side and only the states between chunks
+    along the sequence (three launches)."""
     _need_cuda(proj, gates, bias_i, bias_f, state_c, state_n, state_m, out)
     lib = load_module("matrix_memory")
     n_seqs = batch.seq_slot.numel()
@@ -1074,6 +1079,15 @@ def matrix_memory(proj, q_at, k_at, v_at, gates, bias_i, bias_f, cap, denom_eps,
     for st, shape in ((state_c, (n_heads, value_dim, key_dim)), (state_n, (n_heads, blocks, key_dim)), (state_m, (n_heads, blocks))):
         assert st.dtype == torch.float32 and st.is_contiguous() and tuple(st.shape[1:]) == shape
     assert batch.seq_start.numel() >= n_seqs + 1
+    if ws is not None:
+        max_chunks = -(-batch.n_rows // MATRIX_MEMORY_CHUNK) + n_seqs
+        work = ws.get("memory_chunks", (max_chunks * n_heads * (value_dim * key_dim + key_dim + 4),), torch.float32)
+        _check(lib, lib.abk_matrix_memory_chunks(
+            _p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(q_at), _i(k_at), _i(v_at), _p(gates), _ll(gates.stride(0)),
+            _p(bias_i), _p(bias_f), _f(cap), _f(denom_eps), _f(float(key_dim) ** -0.5), _i(n_heads), _i(key_dim),
+            _i(value_dim), _p(state_c), _p(state_n), _p(state_m), _p(out), _p(batch.seq_start), _p(batch.seq_slot),
+            _i(n_seqs), _i(max_chunks), _p(work), _ll(work.numel()), _stream()), "matrix_memory_chunks", kernels=3)
+        return
     _check(lib, lib.abk_matrix_memory(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(q_at), _i(k_at), _i(v_at), _p(gates),
                                       _ll(gates.stride(0)), _p(bias_i), _p(bias_f), _f(cap), _f(denom_eps),
                                       _f(float(key_dim) ** -0.5), _i(n_heads), _i(key_dim), _i(value_dim), _p(state_c),

@@ -7,7 +7,8 @@ Per head a float32 state C [key, value], n [key] and a running maximum m, all ze
     o = C'^T q / (max(|n' . q|, e^(-m')) + denom_eps),      q = key^-1/2 Wq x
 The mixer owns what stands around it: one stacked product for q, k, v and the output gate, a small product of its own
 for the two gates' pre-activations (float32 out of it: they stand in exponents), the per-head norm of o with its weight
-and sigmoid(Wg x), the output product. It keeps no keys: its cache is the state, and its cost per token does not grow.
+and sigmoid(Wg x), the output product. Steps that bring prompts run the recurrence in chunks of 64 tokens (the same
+numbers, summed in another order); a token a sequence runs it as it stands. It keeps no keys: its cache is the state, and its cost per token does not grow.
 The gates, the state, the read-out, the norm and the gate's sigmoid are float32 in both number formats.
 """
 import torch
@@ -16,6 +17,11 @@ from ..cache.need import CacheNeed
 from ..kernels import ops
 from .base import MIXERS, to_device
 from .linear import Linear
+
+
+# From how many rows of a step on the recurrence runs in chunks (three launches whose work lies side by side) rather than
+# token by token (one launch that walks every sequence).
+CHUNKED_FROM = 32
 
 
 def _up8(n):
@@ -94,7 +100,8 @@ class MatrixMemory:
         o = ws.get("memory_o", (n, self.v_size), torch.float32)
         ops.matrix_memory(proj, 0, self.at_k, self.at_v, gates, self.bias_i, self.bias_f, s.gate_cap, s.denom_eps, s.n_heads,
                           s.key_dim, s.value_dim, cache.states["memory"], cache.states["memory_n"],
-                          cache.states["memory_m"], o, batch)
+                          cache.states["memory_m"], o, batch,
+                          ws=ws if not batch.is_decode and n >= CHUNKED_FROM else None)
         normed = ws.get("memory_normed", (n, self.v_size), dt)
         ops.gated_head_norm(o, proj[:, self.at_g:self.at_g + self.v_size], self.out_norm, normed, n, s.n_heads, s.value_dim,
                             s.norm_eps)
