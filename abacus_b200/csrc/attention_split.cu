@@ -5,7 +5,9 @@
 // unnormalised weighted values of its keys; a second kernel folds a row's parts, the sink among them.
 //
 //   key j is seen from position i when j <= i and (window == 0 or i - j < window or j < keep_first)
+//                                             and (chunk == 0 or j / chunk == i / chunk)
 //   p_j = exp(z_j - M) / (exp(sink - M) + sum_j exp(z_j - M)),  z_j = scale * (q . k_j),  out = sum_j p_j v_j
+//   (with a cap c of the scores, z_j = c tanh(scale * (q . k_j) / c))
 //
 // A row's visible keys are numbered: first the kept first keys the window no longer reaches, then the window's
 // (or all). Part t has numbers [128 t, 128 t + 128). All arithmetic is float32.
@@ -23,7 +25,9 @@ struct AttnSplit {
     void *out;           // [tokens, heads * v_dim]
     int n_heads, n_kv_heads, head_dim, v_dim;
     float scale;
+    float softcap;       // > 0: z <- softcap * tanh(z / softcap), after the scale
     int window, keep_first;
+    int chunk;           // > 0: key j is seen from i only if j / chunk == i / chunk
     const float *sink;
     const int *token_seq, *token_pos, *seq_slot;
     const void *k_pool, *v_pool;
@@ -37,7 +41,18 @@ struct AttnSplit {
 __device__ __forceinline__ void visible_keys(const AttnSplit &p, int pos, int &lo, int &kept, int &total) {
     lo = p.window > 0 && pos - p.window + 1 > 0 ? pos - p.window + 1 : 0;
     kept = p.keep_first < lo ? p.keep_first : lo;
+    if (p.chunk > 0) {  // the token's chunk starts no earlier than any kept first key that lies outside it
+        const int first = pos / p.chunk * p.chunk;
+        if (first > lo) lo = first;
+        if (first > 0) kept = 0;
+    }
     total = kept + pos - lo + 1;
+}
+
+// The score of a product q . k: scaled, then capped where the layer caps its scores.
+__device__ __forceinline__ float score_of(const AttnSplit &p, float dot) {
+    const float z = dot * p.scale;
+    return p.softcap > 0.0f ? p.softcap * tanhf(z / p.softcap) : z;
 }
 
 // q (float32, 16-byte aligned, the same for every thread: a broadcast) . k (this thread's key row)
@@ -154,8 +169,8 @@ template <typename T, bool STAGED, int GMAX, bool TC = false> __global__ void __
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) {
             const int key = warp * 32 + nt * 8 + k0;
-            if (lower) p_s[row * AS_THREADS + key] = acc[nt][0] * p.scale, p_s[row * AS_THREADS + key + 1] = acc[nt][1] * p.scale;
-            if (upper) p_s[(row + 8) * AS_THREADS + key] = acc[nt][2] * p.scale, p_s[(row + 8) * AS_THREADS + key + 1] = acc[nt][3] * p.scale;
+            if (lower) p_s[row * AS_THREADS + key] = score_of(p, acc[nt][0]), p_s[row * AS_THREADS + key + 1] = score_of(p, acc[nt][1]);
+            if (upper) p_s[(row + 8) * AS_THREADS + key] = score_of(p, acc[nt][2]), p_s[(row + 8) * AS_THREADS + key + 1] = score_of(p, acc[nt][3]);
         }
         __syncthreads();
 #pragma unroll
@@ -165,7 +180,7 @@ template <typename T, bool STAGED, int GMAX, bool TC = false> __global__ void __
         const T *k = STAGED ? (const T *)(k_s + tid * k_pitch) : (const T *)p.k_pool + k_off[tid];
 #pragma unroll
         for (int g = 0; g < GMAX; g++)
-            if (g < group) sc[g] = dot_q<T>(q_s + g * hd, k, hd) * p.scale;
+            if (g < group) sc[g] = score_of(p, dot_q<T>(q_s + g * hd, k, hd));
     } else {
 #pragma unroll
         for (int g = 0; g < GMAX; g++) sc[g] = -INFINITY;
@@ -331,7 +346,7 @@ template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_fo
 
 // max_keys: an upper bound of the keys any row of the step sees (its position + 1, or window + keep_first);
 // parts: float32 scratch of at least tokens * heads * ceil(max_keys / 128) * (v_dim + 2).
-static int attention_split(int values_in_keys, const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+static int attention_split(int values_in_keys, int chunk, float softcap, const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
                                    int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
                                    const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
                                    const void *k_pool, const void *v_pool, const int *page_table, int table_width,
@@ -355,6 +370,7 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
     p.q = q, p.q_row = q_row, p.parts = parts, p.out = out, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.head_dim = head_dim, p.v_dim = v_dim, p.scale = scale, p.window = window > 0 ? window : 0;
     p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0, p.sink = sink;
+    p.chunk = chunk > 0 ? chunk : 0, p.softcap = softcap > 0.0f ? softcap : 0.0f;
     p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.k_pool = k_pool, p.v_pool = v_pool;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
@@ -417,8 +433,8 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
                                    const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
                                    const void *k_pool, const void *v_pool, const int *page_table, int table_width,
                                    int ring_pages, int pinned_pages, int tokens_per_page, int max_keys, float *parts,
-                                   long long parts_floats, void *stream) {
-    return attention_split(0, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first,
+                                   long long parts_floats, int chunk, float softcap, void *stream) {
+    return attention_split(0, chunk, softcap, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first,
                            sink, token_seq, token_pos, seq_slot, k_pool, v_pool, page_table, table_width, ring_pages,
                            pinned_pages, tokens_per_page, max_keys, parts, parts_floats, stream);
 }
@@ -431,7 +447,7 @@ extern "C" int abk_attention_split_values_in_keys(const void *q, long long q_row
                                                   const int *seq_slot, const void *k_pool, const int *page_table,
                                                   int table_width, int tokens_per_page, int max_keys, float *parts,
                                                   long long parts_floats, void *stream) {
-    return attention_split(1, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, 0, 0, sink,
+    return attention_split(1, 0, 0.0f, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, 0, 0, sink,
                            token_seq, token_pos, seq_slot, k_pool, k_pool, page_table, table_width, 0, 0, tokens_per_page,
                            max_keys, parts, parts_floats, stream);
 }

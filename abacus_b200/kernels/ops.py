@@ -364,6 +364,11 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     take none of them."""
     if chunk or softcap:  # the general kernel knows chunks and capped scores, and the prompt kernel with float32 weights
         assert prepare is None, "q, k and v must be prepared before this kernel"
+        if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
+                and n_heads // n_kv_heads <= 16 and head_dim % 8 == 0):
+            attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=v_dim,
+                            keep_first=keep_first, sink=sink, row=row, chunk=chunk, softcap=softcap)
+            return
         if (exact_weights and not batch.is_decode and not batch.any_continuation
                 and attention_window_takes(qkv, head_dim, v_dim or head_dim, n_heads, n_kv_heads, row)):
             attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=v_dim,
@@ -433,7 +438,7 @@ def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
 
 
 def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=None, keep_first=0,
-                    sink=None, row=None, max_keys=None):
+                    sink=None, row=None, max_keys=None, chunk=None, softcap=None):
     """One new token per sequence against the paged cache with the general options (see attention_generic), split
     along the keys into parts of 128 that a second kernel folds (csrc/attention_split.cu); softmax weights float32.
     max_keys bounds the keys a row sees (by default the window and its kept keys, or the step's position bound)."""
@@ -450,13 +455,16 @@ def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batc
         raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {top}")
     if max_keys is None:
         max_keys = min(top, window + (keep_first or 0)) if window else top
+        if chunk:
+            max_keys = min(max_keys, chunk)
     n_parts = -(-max_keys // 128)
     parts = ws.get("attention_parts", (n * n_heads * n_parts * (vd + 2),), torch.float32)
     _check(lib, lib.abk_attention_split(
         _p(qkv), _ll(row), _p(out), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(vd), _f(scale),
         _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot),
         _p(cache.k), _p(cache.v), _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages),
-        _i(cache.pinned_pages), _i(cache.tokens_per_page), _i(max_keys), _p(parts), _ll(parts.numel()), _stream()),
+        _i(cache.pinned_pages), _i(cache.tokens_per_page), _i(max_keys), _p(parts), _ll(parts.numel()), _i(chunk or 0),
+        _f(softcap or 0.0), _stream()),
         "attention_split", kernels=2)
 
 
