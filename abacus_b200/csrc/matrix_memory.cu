@@ -257,14 +257,25 @@ __global__ void __launch_bounds__(256) mm_chunk_prefix_kernel(MatrixMemoryChunks
     const long long stride = mc_stride(K, V);
     float *work = p.work + ((long long)chunk0 * p.s.n_heads + h) * stride;
     float x = *own, m = work[(long long)V * K + K + 2];
-    for (int c = 0; c < chunks; c++, work += stride * p.s.n_heads) {
-        float *scalars = work + (long long)V * K + K;
-        const float A = scalars[0], F = scalars[1], M = fmaxf(m, A);
-        const float sum = work[e];
-        work[e] = x;                                  // the chunk's start state, where its sum was
-        x = fmaf(expf(m - M), x, expf(A - M) * sum);
-        if (e == 0 && c > 0) scalars[2] = m;          // (the first chunk's was left by chunk_sums)
-        m = F + M;
+    const long long step = stride * p.s.n_heads;
+    for (int c0 = 0; c0 < chunks; c0 += 4, work += 4 * step) {  // four chunks' loads in flight together
+        float sum[4], A[4], F[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const bool real = c0 + u < chunks;
+            const float *w = work + (real ? u : 0) * step;
+            sum[u] = w[e], A[u] = w[(long long)V * K + K], F[u] = w[(long long)V * K + K + 1];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (c0 + u >= chunks) break;
+            float *w = work + u * step;
+            const float M = fmaxf(m, A[u]);
+            w[e] = x;                                                      // the chunk's start state, where its sum was
+            x = fmaf(expf(m - M), x, expf(A[u] - M) * sum[u]);
+            if (e == 0 && c0 + u > 0) w[(long long)V * K + K + 2] = m;     // (the first chunk's was left by chunk_sums)
+            m = F[u] + M;
+        }
     }
     if (is_n) {
         for (int b = 0; b < blocks; b++) own[(long long)b * K] = x;
@@ -277,10 +288,32 @@ __global__ void __launch_bounds__(256) mm_chunk_prefix_kernel(MatrixMemoryChunks
     }
 }
 
-template <typename T>
+// acc[u] += q . rows[(sg + 4 * (j0 + u))] for u < 4: a token's row against four rows a pitch apart. VEC: the key size is a
+// multiple of 4 and the pitch K + 4, so both sides come as 16-byte pieces (a fifth of the loads a multiply-add).
+template <bool VEC>
+__device__ __forceinline__ void mc_dots(const float *q, const float *rows, int KP, int K, float *acc) {
+    if (VEC) {
+        for (int i = 0; i < K; i += 4) {
+            const float4 qq = *(const float4 *)(q + i);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float4 kk = *(const float4 *)(rows + (long long)u * 4 * KP + i);
+                acc[u] = fmaf(qq.w, kk.w, fmaf(qq.z, kk.z, fmaf(qq.y, kk.y, fmaf(qq.x, kk.x, acc[u]))));
+            }
+        }
+    } else {
+        for (int i = 0; i < K; i++) {
+            const float qq = q[i];
+#pragma unroll
+            for (int u = 0; u < 4; u++) acc[u] = fmaf(qq, rows[(long long)u * 4 * KP + i], acc[u]);
+        }
+    }
+}
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) mm_chunk_outputs_kernel(MatrixMemoryChunks p) {
     extern __shared__ __align__(16) float mc_smem[];
-    const int K = p.s.key, V = p.s.value, h = blockIdx.y, v0 = blockIdx.z * MC_VT_OUT, KP = K + 1;
+    const int K = p.s.key, V = p.s.value, h = blockIdx.y, v0 = blockIdx.z * MC_VT_OUT, KP = VEC ? K + 4 : K + 1;
     float *qs = mc_smem;                          // [MC_TOKENS][KP]
     float *ks = qs + MC_TOKENS * KP;              // [MC_TOKENS][KP]; later the start state's columns [MC_VT_OUT][KP]
     float *ps = ks + MC_TOKENS * KP;              // [MC_TOKENS][MC_TOKENS + 1]: e^(a_s - M_t) (q_t . k_s), 0 for s > t
@@ -311,13 +344,7 @@ __global__ void __launch_bounds__(256) mm_chunk_outputs_kernel(MatrixMemoryChunk
     // the chunk's own scores, weighted
     for (int j0 = 0; j0 < MC_TOKENS / 4; j0 += 4) {
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (sg + 4 * j0 <= t && t < nt) {
-            for (int i = 0; i < K; i++) {
-                const float qq = qs[t * KP + i];
-#pragma unroll
-                for (int u = 0; u < 4; u++) acc[u] = fmaf(qq, ks[(sg + 4 * (j0 + u)) * KP + i], acc[u]);
-            }
-        }
+        if (sg + 4 * j0 <= t && t < nt) mc_dots<VEC>(qs + t * KP, ks + (sg + 4 * j0) * KP, KP, K, acc);
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int s = sg + 4 * (j0 + u);
@@ -344,11 +371,7 @@ __global__ void __launch_bounds__(256) mm_chunk_outputs_kernel(MatrixMemoryChunk
     for (int j0 = 0; j0 < MC_VT_OUT / 4; j0 += 4) {
         if (v0 + sg + 4 * j0 >= V) break;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int i = 0; i < K; i++) {
-            const float qq = qs[t * KP + i];
-#pragma unroll
-            for (int u = 0; u < 4; u++) acc[u] = fmaf(qq, ks[(sg + 4 * (j0 + u)) * KP + i], acc[u]);
-        }
+        mc_dots<VEC>(qs + t * KP, ks + (sg + 4 * j0) * KP, KP, K, acc);
 #pragma unroll
         for (int u = 0; u < 4; u++) acc[u] *= e_t;
         for (int s = 0; s <= t; s++) {
@@ -387,18 +410,21 @@ extern "C" int abk_matrix_memory_chunks(const void *proj, long long ld, int dtyp
     p.work = work, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_a = (size_t)(MC_TOKENS * key + MC_TOKENS * MC_VT_SUMS + 3 * MC_TOKENS) * sizeof(float);
-    const size_t smem_c = (size_t)(2 * MC_TOKENS * (key + 1) + MC_TOKENS * (MC_TOKENS + 1) + MC_TOKENS * MC_VT_OUT + key +
-                                   4 * MC_TOKENS) * sizeof(float);
+    const bool vec = key % 4 == 0;
+    const size_t smem_c = (size_t)(2 * MC_TOKENS * (key + (vec ? 4 : 1)) + MC_TOKENS * (MC_TOKENS + 1) + MC_TOKENS * MC_VT_OUT +
+                                   key + 4 * MC_TOKENS) * sizeof(float);
     const unsigned sums_tiles = (value + MC_VT_SUMS - 1) / MC_VT_SUMS, out_tiles = (value + MC_VT_OUT - 1) / MC_VT_OUT;
     const unsigned elements = (unsigned)(((long long)value * key + key + 255) / 256);
 #define MC_LAUNCH(T)                                                                                             \
     do {                                                                                                         \
         cudaError_t e = abk_allow_shared_memory((const void *)mm_chunk_sums_kernel<T>, (int)smem_a);             \
-        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)mm_chunk_outputs_kernel<T>, (int)smem_c); \
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)mm_chunk_outputs_kernel<T, true>, (int)smem_c); \
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)mm_chunk_outputs_kernel<T, false>, (int)smem_c); \
         if (e != cudaSuccess) return (int)e;                                                                     \
         abk_launch(mm_chunk_sums_kernel<T>, dim3(max_chunks, n_heads, sums_tiles), dim3(256), smem_a, s, p);     \
         abk_launch(mm_chunk_prefix_kernel, dim3(elements, n_heads, n_seqs), dim3(256), 0, s, p);                 \
-        abk_launch(mm_chunk_outputs_kernel<T>, dim3(max_chunks, n_heads, out_tiles), dim3(256), smem_c, s, p);   \
+        if (vec) abk_launch(mm_chunk_outputs_kernel<T, true>, dim3(max_chunks, n_heads, out_tiles), dim3(256), smem_c, s, p); \
+        else abk_launch(mm_chunk_outputs_kernel<T, false>, dim3(max_chunks, n_heads, out_tiles), dim3(256), smem_c, s, p);    \
     } while (0)
     if (dtype == ABK_BF16) MC_LAUNCH(__nv_bfloat16);
     else MC_LAUNCH(float);
