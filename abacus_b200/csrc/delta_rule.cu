@@ -486,6 +486,258 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
     return ABK_LAUNCH_RESULT();
 }
 
+// ------------------------------------------------------------------ one decay a head, prompts: in chunks
+// With one decay g_t for all of a head's key channels the recurrence of a chunk of DC_TOKENS tokens that starts from S0
+// unrolls, G_t the product of the chunk's decays up to t and r(t, s) = G_t / G_s:
+//     u_t = b_t (v_t - G_t S0^T k_t - sum over s < t of r(t, s) (k_s . k_t) u_s)
+//     o_t = G_t S0^T q_t + sum over s <= t of r(t, s) (k_s . q_t) u_s        S_end = G_end S0 + sum_s r(end, s) k_s u_s^T
+// The first line is a triangular system (I + M) U = diag(b) (V - diag(G) K S0), M(t, s) = b_t r(t, s) (k_t . k_s) for
+// s < t, whose matrix knows neither the state nor the values. delta_chunk_tables makes T = (I + M)^-1 diag(b) and
+// Q(t, s) = r(t, s) (q_t . k_s) for every chunk and head side by side; delta_chunk_scan walks a sequence's chunks for one
+// head and DC_VT value columns (the columns of a state do not meet) with four products a chunk:
+//     [K; Q] S0,   U = T (V - diag(G) K S0),   O = diag(G) Q S0 + Q U,   S_end = G_end S0 + K^T diag(r(end, .)) U.
+// Float32 throughout; the same numbers as token by token, summed in another order. A decay below e^-80 counts as e^-80.
+#define DC_TOKENS 64
+#define DC_VT 16
+#define DC_P (DC_TOKENS + 1)
+
+struct DeltaChunks {
+    DeltaScan s;
+    float *work;   // per (chunk, head): T [64][64], Q [64][64], the logarithms of G [64]
+    int n_seqs, max_chunks;
+};
+#define DC_WORK (2 * DC_TOKENS * DC_TOKENS + DC_TOKENS)
+
+__device__ __forceinline__ bool dc_locate(const DeltaChunks &p, int chunk, int &t0, int &nt) {
+    for (int q = 0; q < p.n_seqs; q++) {
+        const int first = p.s.seq_start[q], n = p.s.seq_start[q + 1] - first;
+        const int chunks = (n + DC_TOKENS - 1) / DC_TOKENS;
+        if (chunk < chunks) {
+            t0 = first + chunk * DC_TOKENS, nt = min(DC_TOKENS, n - chunk * DC_TOKENS);
+            return true;
+        }
+        chunk -= chunks;
+    }
+    return false;
+}
+
+// The chunk's k and q rows out of their records into shared memory, [DC_TOKENS][KP], rows beyond nt zero.
+__device__ __forceinline__ void dc_stage_rows(const DeltaScan &p, int h, int t0, int nt, float *ks, float *qs, int KP) {
+    const int K = p.key, region = p.parts * SCAN_RUN;
+    for (int e = threadIdx.x; e < DC_TOKENS * K; e += blockDim.x) {
+        const int t = e / K, i = e - t * K, at = (i / SCAN_ROWS) * SCAN_RUN + i % SCAN_ROWS;
+        const float *rec = p.records + ((long long)(t0 + t) * p.heads + h) * p.record;
+        ks[t * KP + i] = t < nt ? rec[at] : 0.0f;
+        qs[t * KP + i] = t < nt ? rec[region + at] : 0.0f;
+    }
+}
+
+__global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) {
+    extern __shared__ __align__(16) float dc_smem[];
+    const int K = p.s.key, KP = K + 1, h = blockIdx.y, region = p.s.parts * SCAN_RUN, vp = p.s.record - 3 * region - 4;
+    float *ks = dc_smem, *qs = ks + DC_TOKENS * KP;
+    float *m = qs + DC_TOKENS * KP;       // [64][65]: M, strictly below the diagonal
+    float *x = m + DC_TOKENS * DC_P;      // [64][65]: T
+    float *lg = x + DC_TOKENS * DC_P, *beta = lg + DC_TOKENS;
+    pdl_wait();
+    int t0, nt;
+    if (!dc_locate(p, blockIdx.x, t0, nt)) return;
+    dc_stage_rows(p.s, h, t0, nt, ks, qs, KP);
+    if (threadIdx.x < DC_TOKENS) {
+        const float *rec = p.s.records + ((long long)(t0 + min((int)threadIdx.x, nt - 1)) * p.s.heads + h) * p.s.record;
+        lg[threadIdx.x] = threadIdx.x < nt ? fmaxf(logf(rec[2 * region]), -80.0f) : 0.0f;
+        beta[threadIdx.x] = threadIdx.x < nt ? rec[3 * region + vp] : 0.0f;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        for (int t = 0; t < DC_TOKENS; t++) sum += lg[t], lg[t] = sum;   // (beyond nt: the last real one's)
+    }
+    __syncthreads();
+    float *work = p.work + ((long long)blockIdx.x * p.s.heads + h) * DC_WORK;
+    // a thread: one row t and every fourth column s
+    const int t = threadIdx.x >> 2, sg = threadIdx.x & 3;
+    for (int j = 0; j < DC_TOKENS / 4; j++) {
+        const int c = sg + 4 * j;
+        float kk = 0.0f, qk = 0.0f;
+        if (c <= t && t < nt) {
+            for (int i = 0; i < K; i++) {
+                const float kc = ks[c * KP + i];
+                kk = fmaf(ks[t * KP + i], kc, kk), qk = fmaf(qs[t * KP + i], kc, qk);
+            }
+        }
+        const float r = c <= t && t < nt ? expf(lg[t] - lg[c]) : 0.0f;
+        m[t * DC_P + c] = c < t ? beta[t] * r * kk : 0.0f;
+        work[DC_TOKENS * DC_TOKENS + t * DC_TOKENS + c] = r * qk;
+    }
+    __syncthreads();
+    // (I + M) X = diag(b): a thread a column, down its rows
+    if (threadIdx.x < DC_TOKENS) {
+        const int j = threadIdx.x;
+        for (int r = 0; r < DC_TOKENS; r++) {
+            float v = r == j ? beta[j] : 0.0f;
+            if (r > j) {
+                float acc = 0.0f;
+                for (int c = j; c < r; c++) acc = fmaf(m[r * DC_P + c], x[c * DC_P + j], acc);
+                v = -acc;
+            }
+            x[r * DC_P + j] = r >= j ? v : 0.0f;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < DC_TOKENS * DC_TOKENS; e += 256) work[e] = x[(e / DC_TOKENS) * DC_P + e % DC_TOKENS];
+    if (threadIdx.x < DC_TOKENS) work[2 * DC_TOKENS * DC_TOKENS + threadIdx.x] = lg[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
+    extern __shared__ __align__(16) float dc_smem[];
+    const int K = p.s.key, V = p.s.value, KP = K + 1, h = blockIdx.y, seq = blockIdx.x, v0 = blockIdx.z * DC_VT;
+    const int region = p.s.parts * SCAN_RUN;
+    float *st = dc_smem;                          // [K][DC_VT]: the state's columns
+    float *rs = st + K * DC_VT;                   // [64][DC_VT]: V - diag(G) K S0
+    float *us = rs + DC_TOKENS * DC_VT;           // [64][DC_VT]: U
+    float *os = us + DC_TOKENS * DC_VT;           // [64][DC_VT]: diag(G) Q S0
+    float *tt = os + DC_TOKENS * DC_VT;           // [64][65]: T
+    float *aq = tt + DC_TOKENS * DC_P;            // [64][65]: Q
+    float *lg = aq + DC_TOKENS * DC_P;            // [64]
+    float *ks = lg + DC_TOKENS, *qs = ks + DC_TOKENS * KP;
+    pdl_wait();
+    const int first = p.s.seq_start[seq], n = p.s.seq_start[seq + 1] - first;
+    if (n <= 0) return;  // the sequence brings no token: its state stays as it is
+    int chunk = 0;
+    for (int q = 0; q < seq; q++) chunk += (p.s.seq_start[q + 1] - p.s.seq_start[q] + DC_TOKENS - 1) / DC_TOKENS;
+    float *state = p.s.state + ((long long)p.s.seq_slot[seq] * p.s.heads + h) * V * K;
+    for (int e = threadIdx.x; e < K * DC_VT; e += 256) {
+        const int c = e / K, i = e - c * K;
+        st[i * DC_VT + c] = v0 + c < V ? state[(long long)(v0 + c) * K + i] : 0.0f;
+    }
+    for (int t0 = first; t0 < first + n; t0 += DC_TOKENS, chunk++) {
+        const int nt = min(DC_TOKENS, first + n - t0);
+        const float *work = p.work + ((long long)chunk * p.s.heads + h) * DC_WORK;
+        __syncthreads();  // the chunk before has been read
+        dc_stage_rows(p.s, h, t0, nt, ks, qs, KP);
+        for (int e = threadIdx.x; e < DC_TOKENS * DC_TOKENS; e += 256) {
+            const int r = e / DC_TOKENS, c = e - r * DC_TOKENS;
+            tt[r * DC_P + c] = work[e], aq[r * DC_P + c] = work[DC_TOKENS * DC_TOKENS + e];
+        }
+        if (threadIdx.x < DC_TOKENS) lg[threadIdx.x] = work[2 * DC_TOKENS * DC_TOKENS + threadIdx.x];
+        for (int e = threadIdx.x; e < DC_TOKENS * DC_VT; e += 256) {
+            const int t = e / DC_VT, c = e - t * DC_VT;
+            rs[e] = t < nt && v0 + c < V ? p.s.records[((long long)(t0 + t) * p.s.heads + h) * p.s.record + 3 * region + c + v0] : 0.0f;
+        }
+        __syncthreads();
+        {   // [K; Q] S0: a thread one of the 128 rows and 8 columns
+            const int row = threadIdx.x >> 1, cg = (threadIdx.x & 1) * 8, t = row & (DC_TOKENS - 1);
+            const float *a = (row < DC_TOKENS ? ks : qs) + t * KP;
+            float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            for (int i = 0; i < K; i++) {
+                const float w = a[i];
+                const float4 s0 = *(const float4 *)(st + i * DC_VT + cg), s1 = *(const float4 *)(st + i * DC_VT + cg + 4);
+                acc[0] = fmaf(w, s0.x, acc[0]), acc[1] = fmaf(w, s0.y, acc[1]), acc[2] = fmaf(w, s0.z, acc[2]), acc[3] = fmaf(w, s0.w, acc[3]);
+                acc[4] = fmaf(w, s1.x, acc[4]), acc[5] = fmaf(w, s1.y, acc[5]), acc[6] = fmaf(w, s1.z, acc[6]), acc[7] = fmaf(w, s1.w, acc[7]);
+            }
+            const float G = expf(lg[t]);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (row < DC_TOKENS) rs[t * DC_VT + cg + u] -= G * acc[u];
+                else os[t * DC_VT + cg + u] = G * acc[u];
+            }
+        }
+        __syncthreads();
+        const int t = threadIdx.x >> 2, c4 = (threadIdx.x & 3) * 4;   // a thread: one token and 4 columns
+        {   // U = T R
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int c = 0; c <= t; c++) {
+                const float w = tt[t * DC_P + c];
+                const float4 r = *(const float4 *)(rs + c * DC_VT + c4);
+                acc[0] = fmaf(w, r.x, acc[0]), acc[1] = fmaf(w, r.y, acc[1]), acc[2] = fmaf(w, r.z, acc[2]), acc[3] = fmaf(w, r.w, acc[3]);
+            }
+            *(float4 *)(us + t * DC_VT + c4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        __syncthreads();
+        {   // O = diag(G) Q S0 + Q U
+            float4 o = *(const float4 *)(os + t * DC_VT + c4);
+            for (int c = 0; c <= t; c++) {
+                const float w = aq[t * DC_P + c];
+                const float4 u = *(const float4 *)(us + c * DC_VT + c4);
+                o.x = fmaf(w, u.x, o.x), o.y = fmaf(w, u.y, o.y), o.z = fmaf(w, u.z, o.z), o.w = fmaf(w, u.w, o.w);
+            }
+            if (t < nt) {
+                float *out = p.s.out + (long long)(t0 + t) * p.s.heads * V + (long long)h * V + v0 + c4;
+                if (v0 + c4 < V) out[0] = o.x;
+                if (v0 + c4 + 1 < V) out[1] = o.y;
+                if (v0 + c4 + 2 < V) out[2] = o.z;
+                if (v0 + c4 + 3 < V) out[3] = o.w;
+            }
+        }
+        // S_end = G_end S0 + K^T diag(r(end, .)) U: a thread a key channel and 8 columns (its own elements of the state)
+        const float lg_end = lg[nt - 1];
+        for (int i = threadIdx.x >> 1; i < K; i += 128) {
+            const int cg = (threadIdx.x & 1) * 8;
+            float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            for (int c = 0; c < nt; c++) {
+                const float w = ks[c * KP + i] * expf(lg_end - lg[c]);
+                const float4 u0 = *(const float4 *)(us + c * DC_VT + cg), u1 = *(const float4 *)(us + c * DC_VT + cg + 4);
+                acc[0] = fmaf(w, u0.x, acc[0]), acc[1] = fmaf(w, u0.y, acc[1]), acc[2] = fmaf(w, u0.z, acc[2]), acc[3] = fmaf(w, u0.w, acc[3]);
+                acc[4] = fmaf(w, u1.x, acc[4]), acc[5] = fmaf(w, u1.y, acc[5]), acc[6] = fmaf(w, u1.z, acc[6]), acc[7] = fmaf(w, u1.w, acc[7]);
+            }
+            const float G = expf(lg_end);
+#pragma unroll
+            for (int u = 0; u < 8; u++) st[i * DC_VT + cg + u] = fmaf(G, st[i * DC_VT + cg + u], acc[u]);
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < K * DC_VT; e += 256) {
+        const int c = e / K, i = e - c * K;
+        if (v0 + c < V) state[(long long)(v0 + c) * K + i] = st[i * DC_VT + c];
+    }
+}
+
+// The delta rule with one decay a head over a step that brings prompts, in chunks of 64 tokens: the preparation of
+// abk_delta_scan, then the chunks' tables side by side, then the sequences' chunks in order. work: float32 scratch of at
+// least max_chunks * heads * (2 * 64 * 64 + 64), max_chunks >= ceil(tokens / 64) + sequences.
+extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, const void *decay_in, long long ld_decay,
+                                const void *beta_in, long long ld_beta, const float *a_log, const float *dt_bias, float *state,
+                                float *out, const int *token_seq, const int *seq_start, const int *seq_slot, int n_tokens,
+                                int n_seqs, int heads, int kv_heads, int key, int value, float *records,
+                                long long records_floats, int max_chunks, float *work, long long work_floats, void *stream) {
+    if (n_seqs <= 0 || n_tokens <= 0 || max_chunks <= 0) return 0;
+    if (key < 1 || key > 256) ABK_REFUSE("delta rule: key size %d, the kernel takes 1 to 256", key);
+    if (kv_heads < 1 || heads % kv_heads) ABK_REFUSE("delta rule: %d heads do not divide into %d key heads", heads, kv_heads);
+    if (heads > 65535 || n_seqs > 65535 || value > 65535 * DC_VT) ABK_REFUSE("delta rule: %d heads of %d values, %d sequences are more than a grid takes", heads, value, n_seqs);
+    const int parts = delta_parts(key), record = delta_record_floats(key, value);
+    if ((long long)n_tokens * heads * record > records_floats || ((uintptr_t)records & 15))
+        ABK_REFUSE("delta rule: the scratch memory holds %lld floats, the step needs %lld (16-byte aligned)", records_floats,
+                   (long long)n_tokens * heads * record);
+    if ((long long)max_chunks * heads * DC_WORK > work_floats)
+        ABK_REFUSE("delta rule: the chunks' scratch memory holds %lld floats, the step needs %lld", work_floats,
+                   (long long)max_chunks * heads * DC_WORK);
+    cudaStream_t s = (cudaStream_t)stream;
+    DeltaPrepare q;
+    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.ld_decay = ld_decay, q.per_head = 1, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
+    q.dt_bias = dt_bias, q.records = records, q.token_seq = token_seq, q.pairs = (long long)n_tokens * heads;
+    q.heads = heads, q.kv_heads = kv_heads, q.key = key, q.value = value, q.parts = parts, q.record = record;
+    q.q_scale = 1.0f / sqrtf((float)key);
+    const long long blocks = (q.pairs + 3) / 4;
+    if (blocks > 0x7fffffffLL) ABK_REFUSE("delta rule: %lld (token, head) pairs are more than a grid takes", q.pairs);
+    if (dtype == ABK_BF16) abk_launch(delta_prepare_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, s, q);
+    else abk_launch(delta_prepare_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, q);
+    int rc = ABK_LAUNCH_RESULT();
+    if (rc) return rc;
+    DeltaChunks p;
+    p.s.records = records, p.s.state = state, p.s.out = out, p.s.seq_start = seq_start, p.s.seq_slot = seq_slot;
+    p.s.heads = heads, p.s.key = key, p.s.value = value, p.s.parts = parts, p.s.record = record, p.s.col_warps = 1;
+    p.work = work, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
+    const size_t smem_t = (size_t)(2 * DC_TOKENS * (key + 1) + 2 * DC_TOKENS * DC_P + 2 * DC_TOKENS) * sizeof(float);
+    const size_t smem_s = (size_t)(key * DC_VT + 3 * DC_TOKENS * DC_VT + 2 * DC_TOKENS * DC_P + DC_TOKENS + 2 * DC_TOKENS * (key + 1)) * sizeof(float);
+    cudaError_t e = abk_allow_shared_memory((const void *)delta_chunk_tables_kernel, (int)smem_t);
+    if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)delta_chunk_scan_kernel, (int)smem_s);
+    if (e != cudaSuccess) return (int)e;
+    abk_launch(delta_chunk_tables_kernel, dim3(max_chunks, heads), dim3(256), smem_t, s, p);
+    abk_launch(delta_chunk_scan_kernel, dim3(n_seqs, heads, (value + DC_VT - 1) / DC_VT), dim3(256), smem_s, s, p);
+    return ABK_LAUNCH_RESULT();
+}
+
 // ------------------------------------------------------------------ gated per-head norm
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]); one warp per (token, head). A token's
 // gates lie at gate + t * ld_gate, float32 or (TG) in the storage type. act: sigmoid, or (silu) z sigmoid(z). w: [value],

@@ -859,14 +859,19 @@ def short_conv_tail(x, channels, taps, tail, batch):
                                         _stream()), "short_conv_tail")
 
 
+DELTA_CHUNK = 64  # tokens of a chunk of the chunked form (one decay a head)
+
+
 def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim, ws,
-               per_head=False):
+               per_head=False, chunks=False):
     """The gated delta rule over every sequence of the step, token by token, from and into the slots' states (float32
     [slots, heads, value, key]). qkv [tokens, 2 * kv_heads * key + heads * value]: q, k and v after their convolution;
     decay_in float32 [tokens, heads * key] (rows of any pitch) before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
     before the sigmoid; out float32 [tokens, heads * value], not yet normed. per_head: one decay for all key channels of a
     head; decay_in is then [tokens, >= heads] of qkv's type and dt_bias [heads]. Two kernels: every (token, head) is
-    prepared in parallel into scratch memory from ws (a parts.Workspace), then the sequences are walked."""
+    prepared in parallel into scratch memory from ws (a parts.Workspace), then the sequences are walked. chunks (with
+    per_head, for steps that bring prompts): the walk goes in chunks of 64 tokens, a triangular system a chunk solved
+    beside the others and four products a chunk along the sequence (three kernels)."""
     _need_cuda(qkv, decay_in, beta_in, a_log, dt_bias, state, out)
     lib = load_module("delta_rule")
     lib.abk_delta_scan_scratch.restype = ctypes.c_longlong
@@ -883,6 +888,16 @@ def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_head
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == n_heads * value_dim
     records = ws.get("delta_records", (int(lib.abk_delta_scan_scratch(_i(n), _i(n_heads), _i(key_dim), _i(value_dim))),),
                      torch.float32)
+    if chunks:
+        assert per_head, "the chunked form takes one decay a head"
+        max_chunks = -(-n // DELTA_CHUNK) + n_seqs
+        work = ws.get("delta_chunks", (max_chunks * n_heads * (2 * DELTA_CHUNK * DELTA_CHUNK + DELTA_CHUNK),), torch.float32)
+        _check(lib, lib.abk_delta_chunks(
+            _p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)), _p(beta_in),
+            _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq), _p(batch.seq_start),
+            _p(batch.seq_slot), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv_heads), _i(key_dim), _i(value_dim), _p(records),
+            _ll(records.numel()), _i(max_chunks), _p(work), _ll(work.numel()), _stream()), "delta_chunks", kernels=3)
+        return
     _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)),
                                    _i(1 if per_head else 0), _p(beta_in), _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq),
                                    _p(batch.seq_start), _p(batch.seq_slot), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv_heads),

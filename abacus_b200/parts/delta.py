@@ -113,6 +113,11 @@ class ChannelDelta:
         return out
 
 
+# From how many rows of a step on the recurrence with one decay a head runs in chunks of 64 tokens rather than token by
+# token.
+CHUNKED_FROM = 32
+
+
 @MIXERS.register("head_delta")
 class HeadDelta:
     """The gated delta rule with one decay per head (config.specs.HeadDeltaSpec): the recurrence above with
@@ -183,7 +188,8 @@ class HeadDelta:
             ops.short_conv_tail(proj, self.channels, s.conv_taps, tail, batch)
         o = ws.get("delta_o", (n, self.v_size), torch.float32)
         ops.delta_scan(qkv, proj[:, self.at_a:self.at_gate], proj[:, self.at_b:self.at_a], self.decay_log, self.decay_bias,
-                       state, o, batch, s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, ws, per_head=True)
+                       state, o, batch, s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, ws, per_head=True,
+                       chunks=not batch.is_decode and n >= CHUNKED_FROM)
         normed = ws.get("delta_normed", (n, self.v_size), dt)
         ops.gated_head_norm(o, proj[:, self.at_gate:self.at_gate + self.v_size], self.out_norm, normed, n, s.n_heads,
                             s.value_dim, s.norm_eps, silu=True)
