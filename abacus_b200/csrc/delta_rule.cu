@@ -589,52 +589,76 @@ __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) 
     if (threadIdx.x < DC_TOKENS) work[2 * DC_TOKENS * DC_TOKENS + threadIdx.x] = lg[threadIdx.x];
 }
 
+// 16 bytes from global to shared memory, or 16 bytes of zeros.
+__device__ __forceinline__ void dc_copy_16(float *dst, const float *src, bool real) {
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+// The rows of k and q lie in shared memory as in their records: runs of 32 channels with 4 floats of padding (zeros
+// beyond the key size), k's runs and then q's, a row every 2 * region + 4 floats; so a chunk comes in as 16-byte copies
+// that are all in flight together. Channel c of run r is at r * SCAN_RUN + c; the state's columns lie the same way,
+// [run][32][DC_VT], rows beyond the key size zero.
+#define DC_TP (DC_TOKENS + 4)   // a row of T or Q in shared memory
 __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
     extern __shared__ __align__(16) float dc_smem[];
-    const int K = p.s.key, V = p.s.value, KP = K + 1, h = blockIdx.y, seq = blockIdx.x, v0 = blockIdx.z * DC_VT;
-    const int region = p.s.parts * SCAN_RUN;
-    float *st = dc_smem;                          // [K][DC_VT]: the state's columns
-    float *rs = st + K * DC_VT;                   // [64][DC_VT]: V - diag(G) K S0
+    const int K = p.s.key, V = p.s.value, h = blockIdx.y, seq = blockIdx.x, v0 = blockIdx.z * DC_VT;
+    const int parts = p.s.parts, region = parts * SCAN_RUN, RP = 2 * region + 4, vp = p.s.record - 3 * region - 4;
+    float *st = dc_smem;                          // [parts * 32][DC_VT]: the state's columns
+    float *rs = st + parts * SCAN_ROWS * DC_VT;   // [64][DC_VT]: V, then V - diag(G) K S0
     float *us = rs + DC_TOKENS * DC_VT;           // [64][DC_VT]: U
     float *os = us + DC_TOKENS * DC_VT;           // [64][DC_VT]: diag(G) Q S0
-    float *tt = os + DC_TOKENS * DC_VT;           // [64][65]: T
-    float *aq = tt + DC_TOKENS * DC_P;            // [64][65]: Q
-    float *lg = aq + DC_TOKENS * DC_P;            // [64]
-    float *ks = lg + DC_TOKENS, *qs = ks + DC_TOKENS * KP;
+    float *tt = os + DC_TOKENS * DC_VT;           // [64][DC_TP]: T
+    float *aq = tt + DC_TOKENS * DC_TP;           // [64][DC_TP]: Q
+    float *lg = aq + DC_TOKENS * DC_TP;           // [64]
+    float *kq = lg + DC_TOKENS;                   // [64][RP]: k's runs, then q's
     pdl_wait();
     const int first = p.s.seq_start[seq], n = p.s.seq_start[seq + 1] - first;
     if (n <= 0) return;  // the sequence brings no token: its state stays as it is
     int chunk = 0;
     for (int q = 0; q < seq; q++) chunk += (p.s.seq_start[q + 1] - p.s.seq_start[q] + DC_TOKENS - 1) / DC_TOKENS;
     float *state = p.s.state + ((long long)p.s.seq_slot[seq] * p.s.heads + h) * V * K;
-    for (int e = threadIdx.x; e < K * DC_VT; e += 256) {
-        const int c = e / K, i = e - c * K;
-        st[i * DC_VT + c] = v0 + c < V ? state[(long long)(v0 + c) * K + i] : 0.0f;
+    for (int e = threadIdx.x; e < parts * SCAN_ROWS * DC_VT; e += 256) {
+        const int c = e / (parts * SCAN_ROWS), i = e - c * (parts * SCAN_ROWS);
+        st[i * DC_VT + c] = v0 + c < V && i < K ? state[(long long)(v0 + c) * K + i] : 0.0f;
     }
+    const int row_pieces = 2 * region / 4;
     for (int t0 = first; t0 < first + n; t0 += DC_TOKENS, chunk++) {
         const int nt = min(DC_TOKENS, first + n - t0);
         const float *work = p.work + ((long long)chunk * p.s.heads + h) * DC_WORK;
         __syncthreads();  // the chunk before has been read
-        dc_stage_rows(p.s, h, t0, nt, ks, qs, KP);
-        for (int e = threadIdx.x; e < DC_TOKENS * DC_TOKENS; e += 256) {
-            const int r = e / DC_TOKENS, c = e - r * DC_TOKENS;
-            tt[r * DC_P + c] = work[e], aq[r * DC_P + c] = work[DC_TOKENS * DC_TOKENS + e];
+        for (int e = threadIdx.x; e < DC_TOKENS * row_pieces; e += 256) {
+            const int t = e / row_pieces, c = e - t * row_pieces;
+            const float *rec = p.s.records + ((long long)(t0 + min(t, nt - 1)) * p.s.heads + h) * p.s.record;
+            dc_copy_16(kq + t * RP + 4 * c, rec + 4 * c, t < nt);
         }
-        if (threadIdx.x < DC_TOKENS) lg[threadIdx.x] = work[2 * DC_TOKENS * DC_TOKENS + threadIdx.x];
-        for (int e = threadIdx.x; e < DC_TOKENS * DC_VT; e += 256) {
-            const int t = e / DC_VT, c = e - t * DC_VT;
-            rs[e] = t < nt && v0 + c < V ? p.s.records[((long long)(t0 + t) * p.s.heads + h) * p.s.record + 3 * region + c + v0] : 0.0f;
+        for (int e = threadIdx.x; e < DC_TOKENS * (DC_TOKENS / 4); e += 256) {
+            const int r = e / (DC_TOKENS / 4), c = e - r * (DC_TOKENS / 4);
+            dc_copy_16(tt + r * DC_TP + 4 * c, work + r * DC_TOKENS + 4 * c, true);
+            dc_copy_16(aq + r * DC_TP + 4 * c, work + DC_TOKENS * DC_TOKENS + r * DC_TOKENS + 4 * c, true);
         }
+        if (threadIdx.x < DC_TOKENS / 4) dc_copy_16(lg + 4 * threadIdx.x, work + 2 * DC_TOKENS * DC_TOKENS + 4 * threadIdx.x, true);
+        {   // the values' columns: a row is DC_VT / 4 pieces, zeros beyond the record's values and the chunk's tokens
+            const int t = threadIdx.x >> 2, c = (threadIdx.x & 3) * 4;
+            const float *rec = p.s.records + ((long long)(t0 + min(t, nt - 1)) * p.s.heads + h) * p.s.record;
+            dc_copy_16(rs + t * DC_VT + c, rec + 3 * region + min(v0 + c, vp - 4), t < nt && v0 + c < vp);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         {   // [K; Q] S0: a thread one of the 128 rows and 8 columns
             const int row = threadIdx.x >> 1, cg = (threadIdx.x & 1) * 8, t = row & (DC_TOKENS - 1);
-            const float *a = (row < DC_TOKENS ? ks : qs) + t * KP;
+            const float *a = kq + t * RP + (row < DC_TOKENS ? 0 : region);
             float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-            for (int i = 0; i < K; i++) {
-                const float w = a[i];
-                const float4 s0 = *(const float4 *)(st + i * DC_VT + cg), s1 = *(const float4 *)(st + i * DC_VT + cg + 4);
-                acc[0] = fmaf(w, s0.x, acc[0]), acc[1] = fmaf(w, s0.y, acc[1]), acc[2] = fmaf(w, s0.z, acc[2]), acc[3] = fmaf(w, s0.w, acc[3]);
-                acc[4] = fmaf(w, s1.x, acc[4]), acc[5] = fmaf(w, s1.y, acc[5]), acc[6] = fmaf(w, s1.z, acc[6]), acc[7] = fmaf(w, s1.w, acc[7]);
+            for (int r = 0; r < parts; r++) {
+                const float *ar = a + r * SCAN_RUN, *sr = st + r * SCAN_ROWS * DC_VT + cg;
+#pragma unroll 8
+                for (int i = 0; i < SCAN_ROWS; i++) {
+                    const float w = ar[i];
+                    const float4 s0 = *(const float4 *)(sr + i * DC_VT), s1 = *(const float4 *)(sr + i * DC_VT + 4);
+                    acc[0] = fmaf(w, s0.x, acc[0]), acc[1] = fmaf(w, s0.y, acc[1]), acc[2] = fmaf(w, s0.z, acc[2]), acc[3] = fmaf(w, s0.w, acc[3]);
+                    acc[4] = fmaf(w, s1.x, acc[4]), acc[5] = fmaf(w, s1.y, acc[5]), acc[6] = fmaf(w, s1.z, acc[6]), acc[7] = fmaf(w, s1.w, acc[7]);
+                }
             }
             const float G = expf(lg[t]);
 #pragma unroll
@@ -648,7 +672,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
         {   // U = T R
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             for (int c = 0; c <= t; c++) {
-                const float w = tt[t * DC_P + c];
+                const float w = tt[t * DC_TP + c];
                 const float4 r = *(const float4 *)(rs + c * DC_VT + c4);
                 acc[0] = fmaf(w, r.x, acc[0]), acc[1] = fmaf(w, r.y, acc[1]), acc[2] = fmaf(w, r.z, acc[2]), acc[3] = fmaf(w, r.w, acc[3]);
             }
@@ -658,7 +682,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
         {   // O = diag(G) Q S0 + Q U
             float4 o = *(const float4 *)(os + t * DC_VT + c4);
             for (int c = 0; c <= t; c++) {
-                const float w = aq[t * DC_P + c];
+                const float w = aq[t * DC_TP + c];
                 const float4 u = *(const float4 *)(us + c * DC_VT + c4);
                 o.x = fmaf(w, u.x, o.x), o.y = fmaf(w, u.y, o.y), o.z = fmaf(w, u.z, o.z), o.w = fmaf(w, u.w, o.w);
             }
@@ -671,19 +695,18 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
             }
         }
         // S_end = G_end S0 + K^T diag(r(end, .)) U: a thread a key channel and 8 columns (its own elements of the state)
-        const float lg_end = lg[nt - 1];
-        for (int i = threadIdx.x >> 1; i < K; i += 128) {
-            const int cg = (threadIdx.x & 1) * 8;
+        const float lg_end = lg[nt - 1], G_end = expf(lg_end);
+        for (int i = threadIdx.x >> 1; i < parts * SCAN_ROWS; i += 128) {
+            const int cg = (threadIdx.x & 1) * 8, at = (i / SCAN_ROWS) * SCAN_RUN + i % SCAN_ROWS;
             float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             for (int c = 0; c < nt; c++) {
-                const float w = ks[c * KP + i] * expf(lg_end - lg[c]);
+                const float w = kq[c * RP + at] * expf(lg_end - lg[c]);
                 const float4 u0 = *(const float4 *)(us + c * DC_VT + cg), u1 = *(const float4 *)(us + c * DC_VT + cg + 4);
                 acc[0] = fmaf(w, u0.x, acc[0]), acc[1] = fmaf(w, u0.y, acc[1]), acc[2] = fmaf(w, u0.z, acc[2]), acc[3] = fmaf(w, u0.w, acc[3]);
                 acc[4] = fmaf(w, u1.x, acc[4]), acc[5] = fmaf(w, u1.y, acc[5]), acc[6] = fmaf(w, u1.z, acc[6]), acc[7] = fmaf(w, u1.w, acc[7]);
             }
-            const float G = expf(lg_end);
 #pragma unroll
-            for (int u = 0; u < 8; u++) st[i * DC_VT + cg + u] = fmaf(G, st[i * DC_VT + cg + u], acc[u]);
+            for (int u = 0; u < 8; u++) st[i * DC_VT + cg + u] = fmaf(G_end, st[i * DC_VT + cg + u], acc[u]);
         }
     }
     __syncthreads();
@@ -709,8 +732,8 @@ extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, co
     if ((long long)n_tokens * heads * record > records_floats || ((uintptr_t)records & 15))
         ABK_REFUSE("delta rule: the scratch memory holds %lld floats, the step needs %lld (16-byte aligned)", records_floats,
                    (long long)n_tokens * heads * record);
-    if ((long long)max_chunks * heads * DC_WORK > work_floats)
-        ABK_REFUSE("delta rule: the chunks' scratch memory holds %lld floats, the step needs %lld", work_floats,
+    if ((long long)max_chunks * heads * DC_WORK > work_floats || ((uintptr_t)work & 15))
+        ABK_REFUSE("delta rule: the chunks' scratch memory holds %lld floats, the step needs %lld (16-byte aligned)", work_floats,
                    (long long)max_chunks * heads * DC_WORK);
     cudaStream_t s = (cudaStream_t)stream;
     DeltaPrepare q;
@@ -729,7 +752,8 @@ extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, co
     p.s.heads = heads, p.s.key = key, p.s.value = value, p.s.parts = parts, p.s.record = record, p.s.col_warps = 1;
     p.work = work, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
     const size_t smem_t = (size_t)(2 * DC_TOKENS * (key + 1) + 2 * DC_TOKENS * DC_P + 2 * DC_TOKENS) * sizeof(float);
-    const size_t smem_s = (size_t)(key * DC_VT + 3 * DC_TOKENS * DC_VT + 2 * DC_TOKENS * DC_P + DC_TOKENS + 2 * DC_TOKENS * (key + 1)) * sizeof(float);
+    const size_t smem_s = (size_t)(parts * SCAN_ROWS * DC_VT + 3 * DC_TOKENS * DC_VT + 2 * DC_TOKENS * DC_TP + DC_TOKENS +
+                                   DC_TOKENS * (2 * parts * SCAN_RUN + 4)) * sizeof(float);
     cudaError_t e = abk_allow_shared_memory((const void *)delta_chunk_tables_kernel, (int)smem_t);
     if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)delta_chunk_scan_kernel, (int)smem_s);
     if (e != cudaSuccess) return (int)e;
