@@ -202,6 +202,54 @@ def test_the_delta_rule_with_a_decay_per_head_every_way(dtype, H, G, K, V, taps)
     _every_way(run, h, want, dtype, f"delta rule {H}/{G}x{K}x{V}, {taps} taps", portions=(60, 2, 7, 1, 64, 16))
 
 
+def test_the_delta_rule_in_many_chunks_with_decays_from_nothing_to_one():
+    """520 tokens (eight chunks and a ragged one), heads whose decay is all but 1, all but 0 (below what float32 holds
+    over a chunk) and in between, write strengths near 1: whole, and continued from a state in portions that end inside
+    chunks; against the plain recurrence."""
+    from abacus_b200.config.specs import HeadDeltaSpec
+    rng, d, H, G, K, V, taps = np.random.default_rng(8), 32, 4, 2, 24, 20, 3
+    p = _delta(rng, d, H, G, K, V, taps, _rnd("float32"))
+    p["A_log"] = np.array([-9.0, 5.0, 0.0, 2.0], dtype=np.float32)
+    p["dt_bias"] = np.array([-2.0, 3.0, 0.0, 1.0], dtype=np.float32)
+    p["b"] = (p["b"] * 0).astype(np.float32)
+    p["b"][:, 0] = 3.0
+    h = rng.standard_normal((520, d)).astype(np.float32)
+    h[:, 0] = 1.0 + 0.2 * rng.standard_normal(520)  # b = sigmoid(about 3)
+    want, _ = plain.scalar_delta_rule(h.astype(np.float64), {n: t.astype(np.float64) for n, t in p.items()},
+                                      {"heads": H, "kv_heads": G, "dim": K, "vdim": V}, 1e-6, None)
+    run = PartRun(HeadDeltaSpec(hidden=d, n_heads=H, n_kv_heads=G, key_dim=K, value_dim=V, conv_taps=taps, norm_eps=1e-6),
+                  {slot: p[name] for slot, name in _DELTA_SLOTS.items()}, "float32")
+    slot = run.open(dirty=True)
+    _close(run.step([(slot, h)])[0], want, "float32", "delta rule, 520 tokens whole", f32=5e-4)
+    run.cache.close_slot(slot)
+    slot, at, got = run.open(dirty=True), 0, []
+    for size in (100, 1, 200, 33, 186):
+        got.append(run.step([(slot, h[at:at + size])])[0])
+        at += size
+    _close(np.concatenate(got), want, "float32", "delta rule, 520 tokens in portions", f32=5e-4)
+
+
+def test_the_matrix_memory_in_many_chunks():
+    """520 tokens with gates that swing between closed and wide open, whole and in portions that end inside chunks."""
+    from abacus_b200.config.specs import MatrixMemorySpec
+    rng, d, H, K, V = np.random.default_rng(12), 32, 3, 20, 36
+    p = _memory(rng, d, H, K, V, _rnd("float32"))
+    p["i"], p["f"] = (p["i"] * 4).astype(np.float32), (p["f"] * 4).astype(np.float32)
+    h = rng.standard_normal((520, d)).astype(np.float32)
+    want, _ = plain.matrix_memory(h.astype(np.float64), {n: t.astype(np.float64) for n, t in p.items()},
+                                  {"heads": H, "dim": K, "vdim": V, "gate_cap": 15.0}, 1e-5, None)
+    run = PartRun(MatrixMemorySpec(hidden=d, n_heads=H, key_dim=K, value_dim=V, gate_cap=15.0, norm_eps=1e-5),
+                  {slot: p[name] for slot, name in _MEMORY_SLOTS.items()}, "float32")
+    slot = run.open(dirty=True)
+    _close(run.step([(slot, h)])[0], want, "float32", "matrix memory, 520 tokens whole", f32=5e-4)
+    run.cache.close_slot(slot)
+    slot, at, got = run.open(dirty=True), 0, []
+    for size in (100, 1, 200, 33, 186):
+        got.append(run.step([(slot, h[at:at + size])])[0])
+        at += size
+    _close(np.concatenate(got), want, "float32", "matrix memory, 520 tokens in portions", f32=5e-4)
+
+
 def _attention_spec(d, H, G, K, V, scale, taps, chunk, cap):
     from abacus_b200.config.specs import AttentionSpec
     return AttentionSpec(hidden=d, n_heads=H, n_kv_heads=G, head_dim=K, scale=scale, qk_norm_eps=None, position=None,
