@@ -577,6 +577,28 @@ def test_trace_replay_of_a_model_folder(tmp_path):
     assert_logits(np.stack([m.reshape(-1, raw["vocab"])[0] for m in more[1:]]), wa[67:70], "float32", "replayed decode", noise)
 
 
+@pytest.mark.parametrize("width,vocab,ff,expert_ff", [(37, 61, 33, 9), (100, 203, 72, 20)])
+def test_a_width_that_fits_no_vector(tmp_path, width, vocab, ff, expert_ff):
+    """Every size odd or a multiple of 4 at most: width, vocabulary, feed-forwards, heads of 7, 9, 10 and 12 channels with
+    values of 5, 7, 14 and 20; a prompt, then tokens one by one, in float32 against the plain model."""
+    raw = {"architecture": "Linonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 512,
+           "layers": [lm.memory_layer(3, 10, 14, 9.0, lm.dense(ff)),
+                      lm.parallel_layer(lm.left(6, 2, 12, 20, 0.2, 3, 50, 20.0), lm.right(4, 2, 12, 10, 4),
+                                        lm.experts(5, 1, 2, 1.3, expert_ff)),
+                      lm.parallel_layer(lm.left(3, 1, 7, 5, 0.3, 2, 9, 8.0), lm.right(3, 3, 9, 7, 2), lm.dense(ff))],
+           "loop": {"start": 1, "stop": 3, "times": 2}}
+    engine, raw, tensors, _ = _engine(tmp_path, f"odd{width}", "float32", raw=raw, seed=3)
+    rng = np.random.default_rng(1)
+    tokens = [int(t) for t in rng.integers(0, vocab, 200)]
+    want, noise = _oracle(raw, tensors, tokens)
+    slot = engine.open()
+    got = [engine.step([(slot, tokens[:170], list(range(170)))]).cpu().numpy()]
+    got += [engine.step([(slot, [t], [0])]).cpu().numpy() for t in tokens[170:]]
+    engine.close(slot)
+    engine.check_status()
+    assert_logits(np.concatenate(got), want, "float32", f"width {width}", noise)
+
+
 @pytest.mark.parametrize("seed", range(8))
 def test_random_configurations_against_the_plain_model(tmp_path, seed):
     rng = np.random.default_rng(100 + seed)
