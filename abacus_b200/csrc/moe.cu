@@ -47,11 +47,20 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T *x, long 
     for (int e = tid; e < experts; e += MR_THREADS) taken[e] = 0;
     __syncthreads();
     const bool vec = d % 4 == 0 && ((uintptr_t)router & 15) == 0;
-    for (int e = warp; e < experts; e += MR_THREADS / 32) {
-        float acc = 0.0f;
-        lane_dots<1>(router + (long long)e * d, 0, xs, d, lane, vec, &acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+    constexpr int W = MR_THREADS / 32;
+    for (int e = warp; e < experts;) {  // a warp's router rows, up to four at a time so that their loads are in flight together
+        const int left = (experts - e + W - 1) / W, rows = left < 4 ? left : 4;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float *w = router + (long long)e * d;
+        if (rows == 4) lane_dots<4>(w, (long long)W * d, xs, d, lane, vec, acc);
+        else if (rows == 3) lane_dots<3>(w, (long long)W * d, xs, d, lane, vec, acc);
+        else if (rows == 2) lane_dots<2>(w, (long long)W * d, xs, d, lane, vec, acc);
+        else lane_dots<1>(w, 0, xs, d, lane, vec, acc);
+        for (int u = 0; u < rows; u++) {
+            const float sum = warp_sum(acc[u]);
+            if (lane == 0) z[e + u * W] = sum;
+        }
+        e += rows * W;
     }
     __syncthreads();
     if (warp != 0) return;
