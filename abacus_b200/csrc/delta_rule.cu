@@ -503,10 +503,10 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
 
 struct DeltaChunks {
     DeltaScan s;
-    float *work;   // per (chunk, head): T [64][64], Q [64][64], the logarithms of G [64]
-    int n_seqs, max_chunks;
+    float *work;   // per (chunk, head): one table [64][64] (Q on and below the diagonal, T below its diagonal transposed
+    int n_seqs, max_chunks;   // above it), the logarithms of G [64], T's diagonal [64] (the write strengths)
 };
-#define DC_WORK (2 * DC_TOKENS * DC_TOKENS + DC_TOKENS)
+#define DC_WORK (DC_TOKENS * DC_TOKENS + 2 * DC_TOKENS)
 
 __device__ __forceinline__ bool dc_locate(const DeltaChunks &p, int chunk, int &t0, int &nt) {
     for (int q = 0; q < p.n_seqs; q++) {
@@ -568,7 +568,7 @@ __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) 
         }
         const float r = c <= t && t < nt ? expf(lg[t] - lg[c]) : 0.0f;
         m[t * DC_P + c] = c < t ? beta[t] * r * kk : 0.0f;
-        work[DC_TOKENS * DC_TOKENS + t * DC_TOKENS + c] = r * qk;
+        if (c <= t) work[t * DC_TOKENS + c] = r * qk;
     }
     __syncthreads();
     // (I + M) X = diag(b): a thread a column, down its rows
@@ -585,8 +585,14 @@ __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) 
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < DC_TOKENS * DC_TOKENS; e += 256) work[e] = x[(e / DC_TOKENS) * DC_P + e % DC_TOKENS];
-    if (threadIdx.x < DC_TOKENS) work[2 * DC_TOKENS * DC_TOKENS + threadIdx.x] = lg[threadIdx.x];
+    for (int e = threadIdx.x; e < DC_TOKENS * DC_TOKENS; e += 256) {  // T below its diagonal, transposed, above the table's
+        const int r = e / DC_TOKENS, c = e % DC_TOKENS;
+        if (c > r) work[e] = x[c * DC_P + r];
+    }
+    if (threadIdx.x < DC_TOKENS) {
+        work[DC_TOKENS * DC_TOKENS + threadIdx.x] = lg[threadIdx.x];
+        work[DC_TOKENS * DC_TOKENS + DC_TOKENS + threadIdx.x] = beta[threadIdx.x];
+    }
 }
 
 // 16 bytes from global to shared memory, or 16 bytes of zeros.
@@ -608,10 +614,10 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
     float *rs = st + parts * SCAN_ROWS * DC_VT;   // [64][DC_VT]: V, then V - diag(G) K S0
     float *us = rs + DC_TOKENS * DC_VT;           // [64][DC_VT]: U
     float *os = us + DC_TOKENS * DC_VT;           // [64][DC_VT]: diag(G) Q S0
-    float *tt = os + DC_TOKENS * DC_VT;           // [64][DC_TP]: T
-    float *aq = tt + DC_TOKENS * DC_TP;           // [64][DC_TP]: Q
-    float *lg = aq + DC_TOKENS * DC_TP;           // [64]
-    float *kq = lg + DC_TOKENS;                   // [64][RP]: k's runs, then q's
+    float *tq = os + DC_TOKENS * DC_VT;           // [64][DC_TP]: Q on and below the diagonal, T transposed above it
+    float *lg = tq + DC_TOKENS * DC_TP;           // [64], then T's diagonal [64]
+    float *td = lg + DC_TOKENS;
+    float *kq = td + DC_TOKENS;                   // [64][RP]: k's runs, then q's
     pdl_wait();
     const int first = p.s.seq_start[seq], n = p.s.seq_start[seq + 1] - first;
     if (n <= 0) return;  // the sequence brings no token: its state stays as it is
@@ -634,10 +640,9 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
         }
         for (int e = threadIdx.x; e < DC_TOKENS * (DC_TOKENS / 4); e += 256) {
             const int r = e / (DC_TOKENS / 4), c = e - r * (DC_TOKENS / 4);
-            dc_copy_16(tt + r * DC_TP + 4 * c, work + r * DC_TOKENS + 4 * c, true);
-            dc_copy_16(aq + r * DC_TP + 4 * c, work + DC_TOKENS * DC_TOKENS + r * DC_TOKENS + 4 * c, true);
+            dc_copy_16(tq + r * DC_TP + 4 * c, work + r * DC_TOKENS + 4 * c, true);
         }
-        if (threadIdx.x < DC_TOKENS / 4) dc_copy_16(lg + 4 * threadIdx.x, work + 2 * DC_TOKENS * DC_TOKENS + 4 * threadIdx.x, true);
+        if (threadIdx.x < 2 * DC_TOKENS / 4) dc_copy_16(lg + 4 * threadIdx.x, work + DC_TOKENS * DC_TOKENS + 4 * threadIdx.x, true);
         {   // the values' columns: a row is DC_VT / 4 pieces, zeros beyond the record's values and the chunk's tokens
             const int t = threadIdx.x >> 2, c = (threadIdx.x & 3) * 4;
             const float *rec = p.s.records + ((long long)(t0 + min(t, nt - 1)) * p.s.heads + h) * p.s.record;
@@ -672,7 +677,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
         {   // U = T R
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             for (int c = 0; c <= t; c++) {
-                const float w = tt[t * DC_TP + c];
+                const float w = c < t ? tq[c * DC_TP + t] : td[t];
                 const float4 r = *(const float4 *)(rs + c * DC_VT + c4);
                 acc[0] = fmaf(w, r.x, acc[0]), acc[1] = fmaf(w, r.y, acc[1]), acc[2] = fmaf(w, r.z, acc[2]), acc[3] = fmaf(w, r.w, acc[3]);
             }
@@ -682,7 +687,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
         {   // O = diag(G) Q S0 + Q U
             float4 o = *(const float4 *)(os + t * DC_VT + c4);
             for (int c = 0; c <= t; c++) {
-                const float w = aq[t * DC_TP + c];
+                const float w = tq[t * DC_TP + c];
                 const float4 u = *(const float4 *)(us + c * DC_VT + c4);
                 o.x = fmaf(w, u.x, o.x), o.y = fmaf(w, u.y, o.y), o.z = fmaf(w, u.z, o.z), o.w = fmaf(w, u.w, o.w);
             }
@@ -718,7 +723,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(DeltaChunks p) {
 
 // The delta rule with one decay a head over a step that brings prompts, in chunks of 64 tokens: the preparation of
 // abk_delta_scan, then the chunks' tables side by side, then the sequences' chunks in order. work: float32 scratch of at
-// least max_chunks * heads * (2 * 64 * 64 + 64), max_chunks >= ceil(tokens / 64) + sequences.
+// least max_chunks * heads * (64 * 64 + 2 * 64), max_chunks >= ceil(tokens / 64) + sequences.
 extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, const void *decay_in, long long ld_decay,
                                 const void *beta_in, long long ld_beta, const float *a_log, const float *dt_bias, float *state,
                                 float *out, const int *token_seq, const int *seq_start, const int *seq_slot, int n_tokens,
@@ -752,13 +757,19 @@ extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, co
     p.s.heads = heads, p.s.key = key, p.s.value = value, p.s.parts = parts, p.s.record = record, p.s.col_warps = 1;
     p.work = work, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
     const size_t smem_t = (size_t)(2 * DC_TOKENS * (key + 1) + 2 * DC_TOKENS * DC_P + 2 * DC_TOKENS) * sizeof(float);
-    const size_t smem_s = (size_t)(parts * SCAN_ROWS * DC_VT + 3 * DC_TOKENS * DC_VT + 2 * DC_TOKENS * DC_TP + DC_TOKENS +
+    const size_t smem_s = (size_t)(parts * SCAN_ROWS * DC_VT + 3 * DC_TOKENS * DC_VT + DC_TOKENS * DC_TP + 2 * DC_TOKENS +
                                    DC_TOKENS * (2 * parts * SCAN_RUN + 4)) * sizeof(float);
+    // Two CTAs of the walk fit an SM (heads of 128 channels: 111 KB each), which a step of many sequences needs; a step
+    // whose CTAs are fewer than the SMs asks for more than half an SM's shared memory instead, so that each CTA has an SM
+    // to itself (measured, one prompt of 2,048 tokens, 64 CTAs: 3.03 ms a step of four layers against 3.37 when the
+    // scheduler may pair them)
+    size_t smem_walk = smem_s;
+    if ((long long)n_seqs * heads * ((value + DC_VT - 1) / DC_VT) <= abk_sm_count() && smem_walk < 116 * 1024) smem_walk = 116 * 1024;
     cudaError_t e = abk_allow_shared_memory((const void *)delta_chunk_tables_kernel, (int)smem_t);
-    if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)delta_chunk_scan_kernel, (int)smem_s);
+    if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)delta_chunk_scan_kernel, (int)smem_walk);
     if (e != cudaSuccess) return (int)e;
     abk_launch(delta_chunk_tables_kernel, dim3(max_chunks, heads), dim3(256), smem_t, s, p);
-    abk_launch(delta_chunk_scan_kernel, dim3(n_seqs, heads, (value + DC_VT - 1) / DC_VT), dim3(256), smem_s, s, p);
+    abk_launch(delta_chunk_scan_kernel, dim3(n_seqs, heads, (value + DC_VT - 1) / DC_VT), dim3(256), smem_walk, s, p);
     return ABK_LAUNCH_RESULT();
 }
 

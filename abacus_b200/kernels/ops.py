@@ -891,7 +891,7 @@ def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_head
     if chunks:
         assert per_head, "the chunked form takes one decay a head"
         max_chunks = -(-n // DELTA_CHUNK) + n_seqs
-        work = ws.get("delta_chunks", (max_chunks * n_heads * (2 * DELTA_CHUNK * DELTA_CHUNK + DELTA_CHUNK),), torch.float32)
+        work = ws.get("delta_chunks", (max_chunks * n_heads * (DELTA_CHUNK * DELTA_CHUNK + 2 * DELTA_CHUNK),), torch.float32)
         _check(lib, lib.abk_delta_chunks(
             _p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)), _p(beta_in),
             _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq), _p(batch.seq_start),
