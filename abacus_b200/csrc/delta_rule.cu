@@ -521,33 +521,35 @@ __device__ __forceinline__ bool dc_locate(const DeltaChunks &p, int chunk, int &
     return false;
 }
 
-// The chunk's k and q rows out of their records into shared memory, [DC_TOKENS][KP], rows beyond nt zero.
-__device__ __forceinline__ void dc_stage_rows(const DeltaScan &p, int h, int t0, int nt, float *ks, float *qs, int KP) {
-    const int K = p.key, region = p.parts * SCAN_RUN;
-    for (int e = threadIdx.x; e < DC_TOKENS * K; e += blockDim.x) {
-        const int t = e / K, i = e - t * K, at = (i / SCAN_ROWS) * SCAN_RUN + i % SCAN_ROWS;
-        const float *rec = p.records + ((long long)(t0 + t) * p.heads + h) * p.record;
-        ks[t * KP + i] = t < nt ? rec[at] : 0.0f;
-        qs[t * KP + i] = t < nt ? rec[region + at] : 0.0f;
-    }
+// 16 bytes from global to shared memory, or 16 bytes of zeros.
+__device__ __forceinline__ void dc_copy_16(float *dst, const float *src, bool real) {
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
 __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) {
     extern __shared__ __align__(16) float dc_smem[];
-    const int K = p.s.key, KP = K + 1, h = blockIdx.y, region = p.s.parts * SCAN_RUN, vp = p.s.record - 3 * region - 4;
-    float *ks = dc_smem, *qs = ks + DC_TOKENS * KP;
-    float *m = qs + DC_TOKENS * KP;       // [64][65]: M, strictly below the diagonal
-    float *x = m + DC_TOKENS * DC_P;      // [64][65]: T
+    const int h = blockIdx.y, parts = p.s.parts, region = parts * SCAN_RUN, RP = 2 * region + 4, vp = p.s.record - 3 * region - 4;
+    float *kq = dc_smem;                      // [64][RP]: k's runs, then q's, as in the records (see delta_chunk_scan)
+    float *m = kq + DC_TOKENS * RP;           // [64][65]: M, strictly below the diagonal
+    float *x = m + DC_TOKENS * DC_P;          // [64][65]: T
     float *lg = x + DC_TOKENS * DC_P, *beta = lg + DC_TOKENS;
     pdl_wait();
     int t0, nt;
     if (!dc_locate(p, blockIdx.x, t0, nt)) return;
-    dc_stage_rows(p.s, h, t0, nt, ks, qs, KP);
+    const int row_pieces = 2 * region / 4;
+    for (int e = threadIdx.x; e < DC_TOKENS * row_pieces; e += 256) {
+        const int t = e / row_pieces, c = e - t * row_pieces;
+        const float *rec = p.s.records + ((long long)(t0 + min(t, nt - 1)) * p.s.heads + h) * p.s.record;
+        dc_copy_16(kq + t * RP + 4 * c, rec + 4 * c, t < nt);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     if (threadIdx.x < DC_TOKENS) {
         const float *rec = p.s.records + ((long long)(t0 + min((int)threadIdx.x, nt - 1)) * p.s.heads + h) * p.s.record;
         lg[threadIdx.x] = threadIdx.x < nt ? fmaxf(logf(rec[2 * region]), -80.0f) : 0.0f;
         beta[threadIdx.x] = threadIdx.x < nt ? rec[3 * region + vp] : 0.0f;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0) {
         float sum = 0.0f;
@@ -561,9 +563,14 @@ __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) 
         const int c = sg + 4 * j;
         float kk = 0.0f, qk = 0.0f;
         if (c <= t && t < nt) {
-            for (int i = 0; i < K; i++) {
-                const float kc = ks[c * KP + i];
-                kk = fmaf(ks[t * KP + i], kc, kk), qk = fmaf(qs[t * KP + i], kc, qk);
+            const float *kt = kq + t * RP, *kc = kq + c * RP;
+            for (int r = 0; r < parts; r++) {
+#pragma unroll
+                for (int i = r * SCAN_RUN; i < r * SCAN_RUN + SCAN_ROWS; i += 4) {
+                    const float4 a = *(const float4 *)(kc + i), b = *(const float4 *)(kt + i), q = *(const float4 *)(kt + region + i);
+                    kk = fmaf(b.w, a.w, fmaf(b.z, a.z, fmaf(b.y, a.y, fmaf(b.x, a.x, kk))));
+                    qk = fmaf(q.w, a.w, fmaf(q.z, a.z, fmaf(q.y, a.y, fmaf(q.x, a.x, qk))));
+                }
             }
         }
         const float r = c <= t && t < nt ? expf(lg[t] - lg[c]) : 0.0f;
@@ -593,12 +600,6 @@ __global__ void __launch_bounds__(256) delta_chunk_tables_kernel(DeltaChunks p) 
         work[DC_TOKENS * DC_TOKENS + threadIdx.x] = lg[threadIdx.x];
         work[DC_TOKENS * DC_TOKENS + DC_TOKENS + threadIdx.x] = beta[threadIdx.x];
     }
-}
-
-// 16 bytes from global to shared memory, or 16 bytes of zeros.
-__device__ __forceinline__ void dc_copy_16(float *dst, const float *src, bool real) {
-    const int bytes = real ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
 // The rows of k and q lie in shared memory as in their records: runs of 32 channels with 4 floats of padding (zeros
@@ -756,7 +757,7 @@ extern "C" int abk_delta_chunks(const void *qkv, long long ld_qkv, int dtype, co
     p.s.records = records, p.s.state = state, p.s.out = out, p.s.seq_start = seq_start, p.s.seq_slot = seq_slot;
     p.s.heads = heads, p.s.key = key, p.s.value = value, p.s.parts = parts, p.s.record = record, p.s.col_warps = 1;
     p.work = work, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
-    const size_t smem_t = (size_t)(2 * DC_TOKENS * (key + 1) + 2 * DC_TOKENS * DC_P + 2 * DC_TOKENS) * sizeof(float);
+    const size_t smem_t = (size_t)(DC_TOKENS * (2 * parts * SCAN_RUN + 4) + 2 * DC_TOKENS * DC_P + 2 * DC_TOKENS) * sizeof(float);
     const size_t smem_s = (size_t)(parts * SCAN_ROWS * DC_VT + 3 * DC_TOKENS * DC_VT + DC_TOKENS * DC_TP + 2 * DC_TOKENS +
                                    DC_TOKENS * (2 * parts * SCAN_RUN + 4)) * sizeof(float);
     // Two CTAs of the walk fit an SM (heads of 128 channels: 111 KB each), which a step of many sequences needs; a step
