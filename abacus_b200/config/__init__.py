@@ -5,7 +5,8 @@ from .qwen3 import Qwen3Config
 from .temetar import TemetarConfig
 from .movarax import MovaraxConfig
 from .linonex import LinonexConfig
+from .tilulorn import TilulornConfig
 
 __all__ = ["ConfigError", "architecture_names", "architecture_of", "get_architecture", "load_config",
            "read_config_json", "register_architecture", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
-           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig", "MovaraxConfig", "LinonexConfig"]
+           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig", "MovaraxConfig", "LinonexConfig", "TilulornConfig"]

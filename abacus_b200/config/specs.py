@@ -37,6 +37,13 @@ class RotarySpec:
     pairing: str = "half"
     kind: str = "rotary"
     exact_angles: bool = False  # the table's angles are made in float64 before their cosines and sines are rounded
+    # Scaled frequencies (exact_angles only). linear_factor c: every frequency is divided by c. blend (factor, original,
+    # fast, slow), the scaling known as YaRN: with where(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta),
+    # lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), rotary_dim - 1) and
+    # ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i * (1 - ramp_i),
+    # and cosines and sines are multiplied by 0.1 ln(factor) + 1.
+    linear_factor: float = 1.0
+    blend: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -53,6 +60,10 @@ class AttentionSpec:
     projection (slots "conv_q", "conv_k", "conv_v", [channels, taps], the last tap the token's own); the last T - 1
     projected rows are part of the sequence's state. chunk C: key j is seen from i only if i // C == j // C, positions
     counted from the sequence's first token. softcap c: score <- c * tanh(score / c), after the scale.
+    norm_over "projection" (with qk_norm_eps): q and k are each normed over their whole row, all heads at once, with
+    weights of that size (slots "q_norm" [heads * head_dim], "k_norm" [kv_heads * head_dim]), before the rotation.
+    values "keys": there is no value projection; a value head is its key head as projected, before norm and rotation.
+    head_gate: head h's output is multiplied by sigmoid(g_h . x), one number a head (slot "wg", [heads, hidden]).
     """
     hidden: int
     n_heads: int
@@ -69,6 +80,9 @@ class AttentionSpec:
     conv_taps: int = 0
     chunk: Optional[int] = None
     softcap: Optional[float] = None
+    norm_over: str = "head"
+    values: str = "own"
+    head_gate: bool = False
     kind: str = "attention"
 
 
@@ -158,6 +172,8 @@ class LatentAttentionSpec:
     holds [c | r] alone. position: a RotarySpec over (part of) the rot_dim part. sink: a learned score per head that
     joins the softmax's denominator once, unscaled, with no key and no value. shares_latents: the entry has no
     down-projection of its own and reads the cache of the schedule entry it names as its source.
+    q_rank Q: the queries pass a latent of their own, q = Wuq norm(Wdq x; w) (slots "wdq" [Q, hidden], "q_norm" [Q],
+    "wq" [heads * (head_dim + rot_dim), Q]). head_gate: head h's output is multiplied by sigmoid(g_h . x) (slot "wg").
     """
     hidden: int
     n_heads: int
@@ -170,6 +186,8 @@ class LatentAttentionSpec:
     position: Optional[RotarySpec]
     sink: bool = False
     shares_latents: bool = False
+    q_rank: Optional[int] = None
+    head_gate: bool = False
     kind: str = "latent_attention"
 
 
@@ -191,6 +209,26 @@ class DecayAttentionSpec:
 
 
 @dataclass(frozen=True)
+class WkvSpec:
+    """A recurrent mixer: time mixing with a decay per head, key channel and token, and a bonus for the token's own key.
+
+    With x' the token before (zeros at a sequence's start; the last token is part of the state), each of r, k, v, g, w
+    reads a blend of its own, m_s = x + (x' - x) * mu_s (slots "mu_r" ... "mu_w", [hidden]). r, k, v = W. m_.
+    (n_heads x key_dim each), gate = silu(Wg m_g), decay = exp(-exp(W2 tanh(W1 m_w) + w0)) per head and key channel
+    (decay_rank the inner size of that pair of matrices). Per head a float32 state S [key, value], zero at the start:
+        o = (S + diag(u) k v^T)^T r;    S <- diag(decay) S + k v^T
+    with the bonus u [heads, key_dim]. Each head's o is divided by its root mean square (norm_eps), the heads side by
+    side are multiplied by a weight [heads * key_dim] and by the gate, then projected.
+    """
+    hidden: int
+    n_heads: int
+    key_dim: int
+    decay_rank: int
+    norm_eps: float
+    kind: str = "wkv"
+
+
+@dataclass(frozen=True)
 class ExpertSpec:
     """A small feed-forward: down(act(up(x))), or, with activation "silu_gated", down(silu(gate(x)) * up(x))."""
     inter: int
@@ -206,6 +244,8 @@ class RoutedMLPSpec:
     all router outputs, the choice goes by s (plus, with correction, a learned shift per output, slot "correction", that
     the weights do not see) and the weights are the chosen s * weight_scale, not renormalized. identity I: the router has
     experts + I outputs, and the last I stand for experts without tensors whose output is their input.
+    score "table": there is no router; row `token id` of an integer table (slot "table", [vocab, top]) names the token's
+    experts, each with weight 1 / top.
     weight_on "input": the output is sum_e expert_e(w_e x); "output": sum_e w_e expert_e(x). shared (an ExpertSpec or
     None) runs for every token and is added.
     """
@@ -219,6 +259,7 @@ class RoutedMLPSpec:
     correction: bool = False
     weight_scale: float = 1.0
     identity: int = 0
+    vocab: int = 0  # rows of the table (score "table")
     kind: str = "routed_mlp"
 
 
@@ -289,6 +330,14 @@ class PositionEmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class LoopInputSpec:
+    """The frame "loop_input": x = table[token]; the frame keeps x as the embedding left it, and before a schedule entry
+    with `inject` t the stream is made anew from itself and the embedding, x <- Win [x; x_0] + step[t] (slots "loop_in"
+    [hidden, 2 hidden], x first, and "loop_step" [passes, hidden]). passes 0: no such entry, no such tensors."""
+    passes: int = 0
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One entry of the run order.
 
@@ -296,11 +345,13 @@ class ScheduleEntry:
     source: None if the mixer keeps keys/values or state of its own for this
     entry; else the index of an earlier entry whose cache it reads.
     rejoin: right before this entry runs, what the frame kept of the embedding is added to the stream (the frame
-    must keep it).
+    must keep it). inject t: right before this entry runs, the frame makes the stream anew from the stream and the
+    embedding, with its t-th step vector (LoopInputSpec).
     """
     layer: int
     source: Optional[int] = None
     rejoin: bool = False
+    inject: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -543,3 +543,146 @@ extern "C" int abk_advance_decode(const int *token_seq, int *token_pos, int n_ro
     return ABK_LAUNCH_RESULT();
 }
 
+
+// ------------------------------------------------------------------ q and k normed over their whole rows, values that are keys
+// Per token: src row [q (heads * hd) | k (kv heads * hd) | ...] as projected; dst row [q | k | v] for the attention
+// kernels. q and k are each normed over their whole row (all heads at once: w * z / sqrt(mean(z^2) + eps), weights of
+// the row's size), then rotated head by head; a value head is its key head as projected, before norm and rotation.
+// k and v go to the paged cache. A CTA a token; float32 arithmetic.
+struct QkvWhole {
+    const void *src;
+    long long lds;
+    void *dst;
+    long long ldd;
+    int n_heads, n_kv_heads, head_dim;
+    const float *q_norm, *k_norm;  // [heads * hd], [kv heads * hd]; null: no norm
+    float eps;
+    const float *cos, *sin;
+    int rotary_dim, interleaved;
+    void *k_pool, *v_pool;
+    PagedCache cache;
+    const int *token_seq, *token_pos, *seq_slot, *seq_len_after;
+};
+
+template <typename T> __global__ void __launch_bounds__(256) qkv_prep_whole_kernel(QkvWhole p) {
+    extern __shared__ float whole[];  // the token's q and k, float32
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    const int seq = p.token_seq[t];
+    if (seq < 0) return;
+    const int pos = p.token_pos[t], hd = p.head_dim;
+    const int q_size = p.n_heads * hd, k_size = p.n_kv_heads * hd;
+    const T *src = (const T *)p.src + (long long)t * p.lds;
+    T *dst = (T *)p.dst + (long long)t * p.ldd;
+    float sq = 0.0f, sk = 0.0f;
+    for (int j = tid; j < q_size + k_size; j += 256) {
+        const float v = to_float(src[j]);
+        whole[j] = v;
+        if (j < q_size) sq = fmaf(v, v, sq);
+        else sk = fmaf(v, v, sk);
+    }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    const bool keeps = p.k_pool && cache_keeps(p.cache, pos, p.seq_len_after[seq]);
+    const int page = keeps ? cache_page(p.cache, p.seq_slot[seq], pos) : 0;
+    // the values: the keys as they were projected
+    for (int j = tid; j < k_size; j += 256) {
+        const T v = src[q_size + j];
+        dst[q_size + k_size + j] = v;
+        if (keeps) ((T *)p.v_pool)[cache_offset(p.cache, page, j / hd, p.n_kv_heads, pos, hd) + j % hd] = v;
+    }
+    if (p.q_norm) {
+        const float rq = 1.0f / sqrtf(sq / (float)q_size + p.eps), rk = 1.0f / sqrtf(sk / (float)k_size + p.eps);
+        for (int j = tid; j < q_size + k_size; j += 256)
+            whole[j] = j < q_size ? p.q_norm[j] * (whole[j] * rq) : p.k_norm[j - q_size] * (whole[j] * rk);
+    }
+    __syncthreads();
+    if (p.cos) {
+        const int half = p.rotary_dim / 2, heads = p.n_heads + p.n_kv_heads;
+        const float *c = p.cos + (long long)pos * half, *s = p.sin + (long long)pos * half;
+        for (int e = tid; e < heads * half; e += 256) {
+            const int h = e / half, i = e - h * half;
+            const int ia = h * hd + (p.interleaved ? 2 * i : i), ib = h * hd + (p.interleaved ? 2 * i + 1 : i + half);
+            const float a = whole[ia], b = whole[ib];
+            whole[ia] = a * c[i] - b * s[i];
+            whole[ib] = b * c[i] + a * s[i];
+        }
+        __syncthreads();
+    }
+    for (int j = tid; j < q_size + k_size; j += 256) {
+        const T v = from_float<T>(whole[j]);
+        dst[j] = v;
+        if (keeps && j >= q_size) {
+            const int jk = j - q_size;
+            ((T *)p.k_pool)[cache_offset(p.cache, page, jk / hd, p.n_kv_heads, pos, hd) + jk % hd] = v;
+        }
+    }
+}
+
+extern "C" int abk_qkv_prep_whole(const void *src, long long lds, void *dst, long long ldd, int dtype, int n_tokens, int n_heads,
+                                  int n_kv_heads, int head_dim, const int *token_seq, const int *token_pos, const int *seq_slot,
+                                  const int *seq_len_after, const float *q_norm, const float *k_norm, float eps,
+                                  const float *cos, const float *sin, int rotary_dim, int interleaved, void *k_pool,
+                                  void *v_pool, const int *page_table, int table_width, int ring_pages, int tokens_per_page,
+                                  int pinned_pages, void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (cos && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > head_dim))
+        ABK_REFUSE("qkv_prep_whole: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
+    if ((q_norm == nullptr) != (k_norm == nullptr)) ABK_REFUSE("qkv_prep_whole: q and k are normed both or neither");
+    const size_t smem = (size_t)(n_heads + n_kv_heads) * head_dim * sizeof(float);
+    if (smem > 160 * 1024) ABK_REFUSE("qkv_prep_whole: rows of %d elements are more than a CTA holds", (n_heads + n_kv_heads) * head_dim);
+    QkvWhole p;
+    p.src = src, p.lds = lds, p.dst = dst, p.ldd = ldd, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.head_dim = head_dim;
+    p.q_norm = q_norm, p.k_norm = k_norm, p.eps = eps, p.cos = cos, p.sin = sin, p.rotary_dim = rotary_dim;
+    p.interleaved = interleaved, p.k_pool = k_pool, p.v_pool = v_pool;
+    p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
+    p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
+    p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_len_after = seq_len_after;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16) {
+        if (smem > 48 * 1024) {
+            cudaError_t e = abk_allow_shared_memory((const void *)qkv_prep_whole_kernel<__nv_bfloat16>, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        abk_launch(qkv_prep_whole_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, s, p);
+    } else {
+        if (smem > 48 * 1024) {
+            cudaError_t e = abk_allow_shared_memory((const void *)qkv_prep_whole_kernel<float>, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        abk_launch(qkv_prep_whole_kernel<float>, dim3(n_tokens), dim3(256), smem, s, p);
+    }
+    return ABK_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------ a gate per head
+// x[t, h, :] *= sigmoid(gate[t, h]): head h of row t at x + t * ldx + h * size, its gate at gate + t * ldg + h.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_heads_kernel(T *x, long long ldx, const T *gate, long long ldg, int heads, int size,
+                                                         long long total) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const long long per = (long long)heads * size, t = i / per;
+    const int e = (int)(i - t * per), h = e / size;
+    const float g = 1.0f / (1.0f + expf(-to_float(gate[t * ldg + h])));
+    T *at = x + t * ldx + e;
+    *at = from_float<T>(to_float(*at) * g);
+}
+
+extern "C" int abk_gate_heads(void *x, long long ldx, const void *gate, long long ldg, int dtype, int n_tokens, int heads, int size,
+                              void *stream) {
+    const long long total = (long long)n_tokens * heads * size;
+    if (total <= 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) ABK_REFUSE("gate_heads: %lld elements are more than a grid takes", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16)
+        abk_launch(gate_heads_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s, (__nv_bfloat16 *)x, ldx,
+                   (const __nv_bfloat16 *)gate, ldg, heads, size, total);
+    else
+        abk_launch(gate_heads_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, (float *)x, ldx, (const float *)gate, ldg,
+                   heads, size, total);
+    return ABK_LAUNCH_RESULT();
+}

@@ -8,7 +8,7 @@
 // head whose values are the first `rank` elements of its keys; V_h is applied to the weighted sum of latents.
 //
 //   latent_prep   per token: c = w * x / sqrt(mean(x^2) + eps) over the first `rank` columns of the down-projection,
-//                 the rotation of the shared key part and of every query head's rotated part (pairs (2i, 2i+1),
+//                 the rotation of the shared key part and of every query head's rotated part (pairs (2i, 2i+1) or (i, i + rot_dims / 2),
 //                 angle table [position][rot_dims / 2]; elements beyond rot_dims pass unchanged), the cache write,
 //                 and the query parts put where the attention kernel wants them.
 //   head_product  out[t, h, :] = W[h] x[t, h, :] for every head: a product per head with a matrix of its own
@@ -24,6 +24,7 @@ struct LatentPrep {
     long long ldp;       // [rank + rot] from column down_at
     int down_at;
     int n_heads, dim, rot, rank, rot_dims;
+    int interleaved;     // pairs (2i, 2i+1) of the rotated dimensions; 0: pairs (i, i + rot_dims / 2)
     const float *norm_w;  // [rank]
     float eps;
     const float *cos, *sin;  // [positions][rot_dims / 2]
@@ -58,9 +59,10 @@ template <typename T> __global__ void __launch_bounds__(128) latent_prep_kernel(
         T *dst = (T *)p.pool + cache_offset(p.cache, page, 0, 1, pos, p.row);
         for (int i = tid; i < p.rank; i += 128) dst[i] = from_float<T>(to_float(down[i]) * inv * p.norm_w[i]);
         for (int i = tid; i < half; i += 128) {
-            const float u = to_float(down[p.rank + 2 * i]), v = to_float(down[p.rank + 2 * i + 1]);
-            dst[p.rank + 2 * i] = from_float<T>(u * cs[i] - v * sn[i]);
-            dst[p.rank + 2 * i + 1] = from_float<T>(v * cs[i] + u * sn[i]);
+            const int ia = p.interleaved ? 2 * i : i, ib = p.interleaved ? 2 * i + 1 : i + half;
+            const float u = to_float(down[p.rank + ia]), v = to_float(down[p.rank + ib]);
+            dst[p.rank + ia] = from_float<T>(u * cs[i] - v * sn[i]);
+            dst[p.rank + ib] = from_float<T>(v * cs[i] + u * sn[i]);
         }
         for (int i = p.rot_dims + tid; i < p.rot; i += 128) dst[p.rank + i] = down[p.rank + i];
         for (int i = p.rank + p.rot + tid; i < p.row; i += 128) dst[i] = from_float<T>(0.0f);
@@ -70,10 +72,11 @@ template <typename T> __global__ void __launch_bounds__(128) latent_prep_kernel(
     for (int e = tid; e < p.n_heads * half; e += 128) {
         const int h = e / half, i = e - h * half;
         const T *q = src + (long long)h * per_head + p.dim;
-        const float u = to_float(q[2 * i]), v = to_float(q[2 * i + 1]);
+        const int ia = p.interleaved ? 2 * i : i, ib = p.interleaved ? 2 * i + 1 : i + half;
+        const float u = to_float(q[ia]), v = to_float(q[ib]);
         T *d = q_out + (long long)h * p.q_head + p.q_rot_at;
-        d[2 * i] = from_float<T>(u * cs[i] - v * sn[i]);
-        d[2 * i + 1] = from_float<T>(v * cs[i] + u * sn[i]);
+        d[ia] = from_float<T>(u * cs[i] - v * sn[i]);
+        d[ib] = from_float<T>(v * cs[i] + u * sn[i]);
     }
     const int rest = p.rot - p.rot_dims, tail = p.q_head - p.q_rot_at - p.rot;
     for (int e = tid; e < p.n_heads * rest; e += 128) {
@@ -92,7 +95,7 @@ template <typename T> __global__ void __launch_bounds__(128) latent_prep_kernel(
 }
 
 extern "C" int abk_latent_prep(const void *proj, long long ldp, int dtype, int n_tokens, int down_at, int n_heads, int dim,
-                               int rot, int rank, int rot_dims, const float *norm_w, float eps, const float *cos,
+                               int rot, int rank, int rot_dims, int interleaved, const float *norm_w, float eps, const float *cos,
                                const float *sin, void *q_dst, long long ldq, int q_head, int q_rot_at, int copy_plain,
                                void *pool, int row, const int *page_table, int table_width, int tokens_per_page,
                                const int *token_seq, const int *token_pos, const int *seq_slot, void *stream) {
@@ -102,7 +105,7 @@ extern "C" int abk_latent_prep(const void *proj, long long ldp, int dtype, int n
         ABK_REFUSE("latent_prep: a head of %d or a cache row of %d does not hold %d + %d elements", q_head, row, rank, rot);
     LatentPrep p;
     p.proj = proj, p.ldp = ldp, p.down_at = down_at, p.n_heads = n_heads, p.dim = dim, p.rot = rot, p.rank = rank;
-    p.rot_dims = rot_dims, p.norm_w = norm_w, p.eps = eps, p.cos = cos, p.sin = sin, p.q_dst = q_dst, p.ldq = ldq;
+    p.rot_dims = rot_dims, p.interleaved = interleaved, p.norm_w = norm_w, p.eps = eps, p.cos = cos, p.sin = sin, p.q_dst = q_dst, p.ldq = ldq;
     p.q_head = q_head, p.q_rot_at = q_rot_at, p.copy_plain = copy_plain, p.pool = pool, p.row = row;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = 0;
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = 0;
@@ -110,6 +113,39 @@ extern "C" int abk_latent_prep(const void *proj, long long ldp, int dtype, int n
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16) abk_launch(latent_prep_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, p);
     else abk_launch(latent_prep_kernel<float>, dim3(n_tokens), dim3(128), 0, s, p);
+    return ABK_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- the norm of a run of columns
+// dst[t, i] = w[i] * src[t, i] / sqrt(mean_i(src[t, i]^2) + eps) for i < count: a latent normed where it lies among the
+// columns of a product's output (rows of any pitch; dst may be src).
+template <typename T>
+__global__ void __launch_bounds__(128) columns_norm_kernel(const T *src, long long lds, T *dst, long long ldd, int count,
+                                                           const float *w, float eps) {
+    __shared__ float scratch[33];
+    const long long t = blockIdx.x;
+    pdl_wait();
+    const T *s = src + t * lds;
+    T *d = dst + t * ldd;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < count; i += 128) {
+        const float v = to_float(s[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)count + eps);
+    for (int i = threadIdx.x; i < count; i += 128) d[i] = from_float<T>(to_float(s[i]) * inv * w[i]);
+}
+
+extern "C" int abk_columns_norm(const void *src, long long lds, void *dst, long long ldd, int dtype, int n_tokens, int count,
+                                const float *w, float eps, void *stream) {
+    if (n_tokens <= 0 || count <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16)
+        abk_launch(columns_norm_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, (const __nv_bfloat16 *)src, lds,
+                   (__nv_bfloat16 *)dst, ldd, count, w, eps);
+    else
+        abk_launch(columns_norm_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float *)src, lds, (float *)dst, ldd, count, w, eps);
     return ABK_LAUNCH_RESULT();
 }
 

@@ -284,3 +284,35 @@ extern "C" int abk_relu_squared(void *x, int dtype, long long total, void *strea
     else abk_launch(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (float *)x, total);
     return ABK_LAUNCH_RESULT();
 }
+
+// ------------------------------------------------------------------ experts by a table
+// A token's experts by its id: pair t * top + k is expert table[token[t]][k] with weight 1 / top. Rows of padding, tokens
+// outside the table and entries that name no expert give -1 (no expert) and weight 0; the latter two set bit 0 of status.
+__global__ void __launch_bounds__(256) moe_table_kernel(const int *tokens, const int *token_seq, const int *table, int vocab, int experts,
+                                                        int top, int n_pairs, int *pair_expert, float *pair_weight, int *status) {
+    pdl_wait();
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int t = i / top, k = i - t * top;
+    int e = -1;
+    if (token_seq[t] >= 0) {
+        const int tok = tokens[t];
+        if (tok >= 0 && tok < vocab) e = table[(long long)tok * top + k];
+        if (e < 0 || e >= experts) {
+            e = -1;
+            atomicOr(status, 1);
+        }
+    }
+    pair_expert[i] = e;
+    pair_weight[i] = e >= 0 ? 1.0f / (float)top : 0.0f;
+}
+
+extern "C" int abk_moe_table(const int *tokens, const int *token_seq, const int *table, int vocab, int experts, int top,
+                             int n_tokens, int *pair_expert, float *pair_weight, int *status, void *stream) {
+    const long long n_pairs = (long long)n_tokens * top;
+    if (n_pairs <= 0) return 0;
+    if (n_pairs > 0x7fffffffLL) ABK_REFUSE("moe_table: %lld pairs are more than a grid takes", n_pairs);
+    abk_launch(moe_table_kernel, dim3((unsigned)((n_pairs + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, tokens, token_seq,
+               table, vocab, experts, top, (int)n_pairs, pair_expert, pair_weight, status);
+    return ABK_LAUNCH_RESULT();
+}

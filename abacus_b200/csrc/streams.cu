@@ -365,3 +365,46 @@ extern "C" int abk_normed_pair(const float *a, const float *b, const float *wa, 
     abk_launch(normed_pair_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, a, b, wa, wb, out, d, eps, share);
     return ABK_LAUNCH_RESULT();
 }
+
+// ------------------------------------------------------------------ a stream made anew from itself and the embedding
+// Before a pass over a run of layers the stream becomes Win [x; x0] + step: `stream_beside` writes the branch still
+// pending (x += y, one stream) and lays the row [x | x0] out in the product's type; `add_vector` adds the pass's vector
+// to the product's result.
+template <typename T>
+__global__ void __launch_bounds__(256) stream_beside_kernel(float *x, const float *y, const float *x0, T *out, int d, long long total) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / d;
+    const int j = (int)(i - t * d);
+    float v = x[i];
+    if (y) {
+        v += y[i];
+        x[i] = v;
+    }
+    out[t * 2 * d + j] = from_float<T>(v);
+    out[t * 2 * d + d + j] = from_float<T>(x0[i]);
+}
+
+extern "C" int abk_stream_beside(float *x, const float *y, const float *x0, void *out, int dtype, int n_tokens, int d, void *stream) {
+    const long long total = (long long)n_tokens * d;
+    if (total <= 0) return 0;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16) abk_launch(stream_beside_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, x, y, x0, (__nv_bfloat16 *)out, d, total);
+    else abk_launch(stream_beside_kernel<float>, grid, dim3(256), 0, s, x, y, x0, (float *)out, d, total);
+    return ABK_LAUNCH_RESULT();
+}
+
+__global__ void __launch_bounds__(256) add_vector_kernel(float *x, const float *v, int d, long long total) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < total) x[i] += v[i % d];
+}
+
+extern "C" int abk_add_vector(float *x, const float *v, int n_tokens, int d, void *stream) {
+    const long long total = (long long)n_tokens * d;
+    if (total <= 0) return 0;
+    abk_launch(add_vector_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, v, d, total);
+    return ABK_LAUNCH_RESULT();
+}

@@ -122,6 +122,8 @@ class CStep:
         for b in model.blocks:
             if type(b) is not PreNormBlock or type(b.mixer) is not Attention or type(b.ffn) is not GatedMLP:
                 return False
+            if b.mixer.whole or b.mixer.spec.head_gate:  # (options the walker's attention entry does not carry)
+                return False
             if type(b.mixer_norm) is not RMSNorm or type(b.ffn_norm) is not RMSNorm:
                 return False
         return model.ctx.dtype in (torch.bfloat16, torch.float32) and model.ctx.device.type == "cuda"

@@ -25,7 +25,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_generic", "attention_decode", "attention_mma", "gemm_rows",
            "sampling", "attention_decode_static", "attention_decode_ring", "attention_tc", "utility", "step", "streams",
-           "delta_rule", "attention_window", "attention_split", "latent", "lightning", "moe", "gemm_grouped", "matrix_memory")
+           "delta_rule", "attention_window", "attention_split", "latent", "lightning", "moe", "gemm_grouped", "matrix_memory", "wkv")
 
 
 # ABACUS_TRACE=1 builds every library with the launch-timeline records of csrc/common.cuh compiled in

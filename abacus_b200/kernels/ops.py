@@ -922,10 +922,11 @@ def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps, sil
 
 # ------------------------------------------------------------------ latent attention (csrc/latent.cu)
 def latent_prep(proj, down_at, n_heads, dim, rot, rank, rot_dims, norm_w, eps, cos, sin, q_dst, q_head, q_rot_at, copy_plain,
-                cache, batch):
+                cache, batch, interleaved=True):
     """What stands between the projections of a latent-attention layer and its attention kernel, per token: the
     latent c = norm_w * z / sqrt(mean(z^2) + eps) over the first `rank` columns of the down-projection (proj[:,
-    down_at:]), the rotation (pairs (2i, 2i+1) of the first rot_dims elements) of the shared key part behind it and of
+    down_at:]), the rotation (pairs (2i, 2i+1), or with interleaved False (i, i + rot_dims / 2), of the first rot_dims
+    elements) of the shared key part behind it and of
     every query head's rotated part (proj[:, h * (dim + rot) + dim:]), the row [c | r | zeros] written to the cache
     (cache: a cache.LayerKV whose rows hold at least rank + rot elements; None: the entry reads another's cache), and
     the query parts put into q_dst: head h of a row at h * q_head, its rotated part at + q_rot_at (zeros behind it up
@@ -944,7 +945,8 @@ def latent_prep(proj, down_at, n_heads, dim, rot, rank, rot_dims, norm_w, eps, c
         assert norm_w.dtype == torch.float32 and norm_w.numel() == rank
     _check(lib, lib.abk_latent_prep(
         _p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(n), _i(down_at), _i(n_heads), _i(dim), _i(rot), _i(rank),
-        _i(rot_dims), _p(norm_w), _f(eps), _p(cos), _p(sin), _p(q_dst), _ll(q_dst.stride(0)), _i(q_head), _i(q_rot_at),
+        _i(rot_dims), _i(1 if interleaved else 0), _p(norm_w), _f(eps), _p(cos), _p(sin), _p(q_dst), _ll(q_dst.stride(0)),
+        _i(q_head), _i(q_rot_at),
         _i(1 if copy_plain else 0), _p(cache.k if cache is not None else None),
         _i(cache.k.shape[-1] if cache is not None else 0), _p(cache.page_table if cache is not None else None),
         _i(cache.table_width if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
@@ -1258,3 +1260,138 @@ def moe_unsort(sorted_out, place, out, n, top, add):
     assert sorted_out.shape[1] == d and place.dtype == torch.int32 and place.numel() >= n * top and out.shape[0] >= n
     _check(lib, lib.abk_moe_unsort(_p(sorted_out), _p(place), _p(out), _i(n), _i(d), _i(top), _i(1 if add else 0), _stream()),
            "moe_unsort")
+
+
+def columns_norm(src, dst, count, weight, eps, n):
+    """dst[t, i] = weight[i] * src[t, i] / sqrt(mean_i(src[t, i]^2) + eps) for i < count, t < n: a run of columns normed
+    where it lies in a product's output (rows of any pitch; dst may be src)."""
+    _need_cuda(src, dst, weight)
+    lib = load_module("latent")
+    assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and src.shape[1] >= count <= dst.shape[1]
+    assert weight.dtype == torch.float32 and weight.numel() == count and src.shape[0] >= n and dst.shape[0] >= n
+    _check(lib, lib.abk_columns_norm(_p(src), _ll(src.stride(0)), _p(dst), _ll(dst.stride(0)), _i(_dt(src)), _i(n), _i(count),
+                                     _p(weight), _f(eps), _stream()), "columns_norm")
+
+
+# ------------------------------------------------------------------ attention whose values are its keys (csrc/elementwise.cu)
+def qkv_prep_whole(src, dst, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved,
+                   cache):
+    """Between the q/k product and attention where q and k are each normed over their whole row (q_norm float32
+    [heads * head_dim], k_norm [kv heads * head_dim]; None: no norm) and a value head is its key head as projected:
+    src rows [q | k | ...] as projected, dst rows [q | k | v] normed, rotated (pairs of the first rotary_dim elements
+    of every head) and, for k and v, written to the cache (a cache.LayerKV, or None)."""
+    _need_cuda(src, dst, q_norm, k_norm, cos, sin)
+    lib = load_module("elementwise")
+    n = batch.n_rows
+    heads_size = (n_heads + 2 * n_kv_heads) * head_dim
+    assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and src.data_ptr() != dst.data_ptr()
+    assert src.shape[1] >= (n_heads + n_kv_heads) * head_dim and dst.shape[1] >= heads_size and min(src.shape[0], dst.shape[0]) >= n
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rotary_dim // 2
+        if batch.max_position >= cos.shape[0]:
+            raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
+    if q_norm is not None:
+        assert q_norm.dtype == k_norm.dtype == torch.float32
+        assert q_norm.numel() == n_heads * head_dim and k_norm.numel() == n_kv_heads * head_dim
+    if cache is not None:
+        assert cache.k.dtype == dst.dtype and cache.k.shape[1:] == (n_kv_heads, cache.tokens_per_page, head_dim)
+        assert cache.v.shape == cache.k.shape
+    _check(lib, lib.abk_qkv_prep_whole(
+        _p(src), _ll(src.stride(0)), _p(dst), _ll(dst.stride(0)), _i(_dt(dst)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim),
+        _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_len_after), _p(q_norm), _p(k_norm),
+        _f(eps or 0.0), _p(cos), _p(sin), _i(rotary_dim), _i(1 if interleaved else 0),
+        _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
+        _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
+        _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
+        _i(cache.pinned_pages if cache is not None else 0), _stream()), "qkv_prep_whole")
+
+
+def gate_heads(x, gate, heads, size, n):
+    """x[t, h * size : (h + 1) * size] *= sigmoid(gate[t, h]) for t < n: a gate per head (rows of any pitch)."""
+    _need_cuda(x, gate)
+    lib = load_module("elementwise")
+    assert x.dtype == gate.dtype and x.stride(1) == 1 and gate.stride(1) == 1
+    assert x.shape[1] >= heads * size and gate.shape[1] >= heads and x.shape[0] >= n and gate.shape[0] >= n
+    _check(lib, lib.abk_gate_heads(_p(x), _ll(x.stride(0)), _p(gate), _ll(gate.stride(0)), _i(_dt(x)), _i(n), _i(heads),
+                                   _i(size), _stream()), "gate_heads")
+
+
+# ------------------------------------------------------------------ the wkv mixer (csrc/wkv.cu)
+def token_shift(x, mu, last, out, batch):
+    """out[s, t] = x[t] + (x'[t] - x[t]) * mu[s]: the blends of every row with the row before it. x [tokens, d] as
+    stored; mu float32 [blends, d]; last float32 [slots, d], the last row each sequence brought in earlier steps (what a
+    step's first row of a sequence takes as x'); out [blends, tokens, d] of x's type. A step of one token a sequence also
+    leaves the new last rows; a step of prompts does so in a second launch."""
+    _need_cuda(x, mu, last, out)
+    lib = load_module("wkv")
+    n, d = batch.n_rows, x.shape[1]
+    blends = mu.shape[0]
+    assert x.is_contiguous() and out.is_contiguous() and out.dtype == x.dtype and out.shape[0] == blends and out.shape[2] == d
+    assert out.shape[1] >= n and mu.dtype == last.dtype == torch.float32 and mu.is_contiguous() and last.is_contiguous()
+    assert mu.shape[1] == d and last.shape[1] == d
+    _check(lib, lib.abk_token_shift(_p(x), _i(_dt(x)), _i(n), _i(d), _p(mu), _i(blends), _p(last), _p(out), _ll(out.stride(0)),
+                                    _i(1 if batch.is_decode else 0), _p(batch.token_seq), _p(batch.seq_start),
+                                    _p(batch.seq_slot), _stream()), "token_shift")
+    if not batch.is_decode:
+        _check(lib, lib.abk_token_shift_keep(_p(x), _i(_dt(x)), _i(d), _p(last), _p(batch.seq_start), _p(batch.seq_slot),
+                                             _i(batch.seq_slot.numel()), _stream()), "token_shift_keep")
+
+
+def tanh_rows(src, dst, n):
+    """dst[:n] = tanh(src[:n]): src float32, dst float32 or bfloat16, both contiguous and of one shape."""
+    _need_cuda(src, dst)
+    lib = load_module("wkv")
+    assert src.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous() and src.shape == dst.shape
+    _check(lib, lib.abk_tanh_rows(_p(src), _p(dst), _i(_dt(dst)), _ll(n * src.shape[1]), _stream()), "tanh_rows")
+
+
+def wkv_scan(proj, r_at, k_at, v_at, n_heads, dim, pre, w0, bonus, state, out, batch):
+    """The recurrence of a wkv layer for every sequence of the step and every head, float32:
+        o = (S + diag(bonus) k v^T)^T r;    S <- diag(exp(-exp(pre + w0))) S + k v^T
+    proj [tokens, .] as stored: r, k, v of head h at columns r_at / k_at / v_at + h * dim; pre float32 [tokens, heads * dim];
+    w0, bonus float32 [heads * dim]; state float32 [slots, heads, dim, dim] (key, value); out float32 [tokens, heads * dim]."""
+    _need_cuda(proj, pre, w0, bonus, state, out)
+    lib = load_module("wkv")
+    hk = n_heads * dim
+    assert proj.stride(1) == 1 and pre.dtype == w0.dtype == bonus.dtype == state.dtype == out.dtype == torch.float32
+    assert pre.is_contiguous() and out.is_contiguous() and state.is_contiguous() and pre.shape[1] == out.shape[1] == hk
+    assert w0.numel() == bonus.numel() == hk and state.shape[1:] == (n_heads, dim, dim)
+    assert proj.shape[1] >= max(r_at, k_at, v_at) + hk
+    _check(lib, lib.abk_wkv_scan(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(r_at), _i(k_at), _i(v_at), _i(n_heads), _i(dim),
+                                 _p(pre), _p(w0), _p(bonus), _p(state), _p(out), _p(batch.seq_start), _p(batch.seq_slot),
+                                 _i(batch.seq_slot.numel()), _stream()), "wkv_scan")
+
+
+# ------------------------------------------------------------------ experts by a table (csrc/moe.cu)
+def moe_table(batch, table, experts, top, pair_expert, pair_weight, status):
+    """pair t * top + k is expert table[token[t], k] with weight 1 / top (table int32 [vocab, top]); rows of padding get -1.
+    An entry that names no expert sets bit 0 of status."""
+    _need_cuda(table, pair_expert, pair_weight, status)
+    lib = load_module("moe")
+    n = batch.n_rows
+    assert table.dtype == torch.int32 and table.is_contiguous() and table.shape[1] == top
+    assert pair_expert.dtype == torch.int32 and pair_weight.dtype == torch.float32 and pair_expert.numel() >= n * top
+    _check(lib, lib.abk_moe_table(_p(batch.tokens), _p(batch.token_seq), _p(table), _i(table.shape[0]), _i(experts), _i(top),
+                                  _i(n), _p(pair_expert), _p(pair_weight), _p(status), _stream()), "moe_table")
+
+
+# ------------------------------------------------------------------ a stream made anew before a pass (csrc/streams.cu)
+def stream_beside(x, y, x0, out, n):
+    """x += y (y None: nothing pending); out[t] = [x[t] | x0[t]] in out's type: the stream beside the embedding, as the
+    input of the product that makes the stream anew. x float32 [tokens, 1, d] or [tokens, d], x0 float32 [tokens, d]."""
+    _need_cuda(x, y, x0, out)
+    lib = load_module("streams")
+    d = x0.shape[1]
+    assert x.dtype == x0.dtype == torch.float32 and x.is_contiguous() and x0.is_contiguous() and out.is_contiguous()
+    assert x.numel() // x.shape[0] == d and out.shape[1] == 2 * d and min(x.shape[0], x0.shape[0], out.shape[0]) >= n
+    assert y is None or (y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == d and y.shape[0] >= n)
+    _check(lib, lib.abk_stream_beside(_p(x), _p(y), _p(x0), _p(out), _i(_dt(out)), _i(n), _i(d), _stream()), "stream_beside")
+
+
+def add_vector(x, v, n):
+    """x[t] += v for t < n (float32; x rows of v's size)."""
+    _need_cuda(x, v)
+    lib = load_module("streams")
+    d = v.numel()
+    assert x.dtype == v.dtype == torch.float32 and x.is_contiguous() and v.is_contiguous() and x.numel() // x.shape[0] == d
+    _check(lib, lib.abk_add_vector(_p(x), _p(v), _i(n), _i(d), _stream()), "add_vector")

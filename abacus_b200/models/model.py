@@ -59,6 +59,8 @@ class Model:
                                  "which must be an earlier entry with a cache of its own")
             if e.rejoin and not hasattr(self.frame, "rejoin"):
                 raise ValueError(f"schedule entry {i} joins the embedding again, which the frame {spec.frame!r} cannot do")
+            if getattr(e, "inject", None) is not None and not hasattr(self.frame, "inject"):
+                raise ValueError(f"schedule entry {i} starts a pass, which the frame {spec.frame!r} cannot do")
         self.ws = Workspace(self.ctx.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.ctx.device)
 
@@ -117,5 +119,7 @@ class Model:
         for i, entry in enumerate(self.schedule):
             if entry.rejoin:  # the embedding joins the stream again (the branch still pending is added after it)
                 self.frame.rejoin(x, batch)
+            if entry.inject is not None:  # a pass starts: the frame makes the stream anew from itself and the embedding
+                y = self.frame.inject(x, y, batch, ws, entry.inject)
             y = self.blocks[entry.layer].forward(x, y, batch, cache.views[i], ws)
         return self.frame.logits(x, y, batch, ws)

@@ -42,8 +42,17 @@ class Attention:
         if s.keep_first and s.window is None:
             raise ValueError("keep_first goes with a window")
         # what only the general kernel takes: values of another size, kept first keys, a sink, float32 weights
+        # q and k normed over their whole rows, values that are their keys, a gate per head: a preparation kernel of
+        # their own (out of the projection's rows into the rows the attention kernels read), then the general kernels
+        self.whole = s.norm_over == "projection" or s.values == "keys"
+        if s.norm_over not in ("head", "projection") or s.values not in ("own", "keys"):
+            raise ValueError(f"norm_over {s.norm_over!r} is neither head nor projection, or values {s.values!r} neither own nor keys")
+        if self.whole and (s.conv_taps or (s.v_head_dim or s.head_dim) != s.head_dim
+                           or (s.qk_norm_eps is not None and s.norm_over != "projection")):
+            raise ValueError("values that are their keys and norms over the whole projection go with neither a convolution, "
+                             "values of another size nor a norm per head")
         self.general = (self.v_dim != s.head_dim or bool(s.keep_first) or s.sink or s.exact_weights or s.conv_taps > 0
-                        or bool(s.chunk) or bool(s.softcap))
+                        or bool(s.chunk) or bool(s.softcap) or self.whole or s.head_gate)
         if s.conv_taps < 0 or s.conv_taps > 8:
             raise ValueError(f"conv_taps {s.conv_taps}: the convolution takes 1 to 8 taps")
         if s.chunk is not None and s.chunk < 1:
@@ -60,6 +69,10 @@ class Attention:
         # a row of q, k and v is padded to a multiple of 8 elements, so that every row starts 16-byte aligned whatever
         # the values' size (nothing to pad where values are as large as keys: head_dim is a multiple of 8)
         self.row = -(-(self.q_size + self.kv_size + self.v_size) // 8) * 8
+        # a row of the stacked product: q, k, v (if projected), then the heads' gates from a multiple of 8 on
+        own_v = self.v_size if s.values == "own" else 0
+        self.gate_at = -(-(self.q_size + self.kv_size + own_v) // 8) * 8
+        self.proj_row = self.gate_at + (-(-s.n_heads // 8) * 8 if s.head_gate else 0) if (self.whole or s.head_gate) else self.row
         self.cos = self.sin = None
         # A step of several tokens of a windowed layer is checked on the host (it may have to be refused): such steps
         # cannot be replayed from a captured graph; single-token steps can. A layer with the general options decides on
@@ -80,7 +93,13 @@ class Attention:
         s = self.spec
         shapes = {"wq": (self.q_size, s.hidden), "wk": (self.kv_size, s.hidden), "wv": (self.v_size, s.hidden),
                   "wo": (s.hidden, s.n_heads * self.v_dim)}
-        if s.qk_norm_eps is not None:
+        if s.values == "keys":
+            del shapes["wv"]
+        if s.head_gate:
+            shapes["wg"] = (s.n_heads, s.hidden)
+        if s.qk_norm_eps is not None and s.norm_over == "projection":
+            shapes.update(q_norm=(self.q_size,), k_norm=(self.kv_size,))
+        elif s.qk_norm_eps is not None:
             shapes.update(q_norm=(s.head_dim,), k_norm=(s.head_dim,))
         if s.sink:
             shapes["sink"] = (s.n_heads,)
@@ -91,9 +110,11 @@ class Attention:
 
     def bind(self, params, ctx):
         self.ctx = ctx
-        wqkv = torch.cat([params["wq"], params["wk"], params["wv"]], dim=0)
-        if self.row > wqkv.shape[0]:
-            wqkv = torch.cat([wqkv, torch.zeros((self.row - wqkv.shape[0], wqkv.shape[1]), dtype=wqkv.dtype)], dim=0)
+        wqkv = torch.cat([params["wq"], params["wk"]] + ([params["wv"]] if "wv" in params else []), dim=0)
+        if self.proj_row > wqkv.shape[0]:
+            wqkv = torch.cat([wqkv, torch.zeros((self.proj_row - wqkv.shape[0], wqkv.shape[1]), dtype=wqkv.dtype)], dim=0)
+        if self.spec.head_gate:
+            wqkv[self.gate_at:self.gate_at + self.spec.n_heads] = params["wg"]
         self.qkv_proj = Linear(to_device(wqkv, ctx, ctx.dtype))
         self.q_proj = Linear(self.qkv_proj.weight[:self.q_size])  # for entries that read another entry's cache
         self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
@@ -137,6 +158,20 @@ class Attention:
             ops.gemm_tc_qkv(xn, w, qkv, s.n_heads, s.n_kv_heads, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
                             self.cos, self.sin, cache.kv, n)
             prepared = True
+        elif self.whole or s.head_gate:
+            # the projection into rows of its own (q, k, v if projected, the heads' gates); q, k and v go from there
+            # into the rows the attention kernels read
+            proj = ws.get("qkv_proj", (n, self.proj_row), self.ctx.dtype)
+            if writes:
+                self.qkv_proj.forward(xn, proj, n)
+            else:
+                raise ops.KernelRefused("an attention entry whose values are its keys, or with gated heads, keeps keys of its own")
+            if self.whole:
+                ops.qkv_prep_whole(proj, qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm,
+                                   s.qk_norm_eps, self.cos, self.sin, rotary_dim, interleaved, cache.kv)
+                prepared = True
+            else:
+                qkv[:n, :self.gate_at].copy_(proj[:n, :self.gate_at])
         elif writes and self.conv is not None:
             # the projection, then the convolution over time into the row the kernels read; the slot's tail follows
             proj = ws.get("qkv_proj", (n, self.row), self.ctx.dtype)
@@ -171,5 +206,7 @@ class Attention:
                       from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare,
                       v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights,
                       row=self.row if self.general else None, chunk=s.chunk, softcap=s.softcap)
+        if s.head_gate:  # head h's output times sigmoid(g_h . x)
+            ops.gate_heads(att, ws.get("qkv_proj", (n, self.proj_row), self.ctx.dtype)[:, self.gate_at:], s.n_heads, self.v_dim, n)
         self.o_proj.forward(att, out, n)
         return out

@@ -174,3 +174,73 @@ class PositionsFrame:
             read_streams(x, pending, self.ones, self.final_norm, xn, rows=batch.logit_rows, n_rows=r)
             self.head.forward(xn, out, r)
         return out
+
+
+@FRAMES.register("loop_input")
+class LoopInputFrame:
+    """x = table[token], unscaled; the stream is [rows, 1, hidden] (parts/streams.py). Where the schedule goes through a
+    run of layers in passes (config.specs.LoopInputSpec), the frame keeps the embedding x_0 and, right before the entry
+    that starts pass t, makes the stream anew from itself and the embedding: x <- Win [x; x_0] + step[t] (the branch
+    still pending is written first; the product's operands are of the model's type, its sums and the stream float32).
+    The end is the plain frame's: the pending branch, the last norm, the output matrix on the wanted rows."""
+    capturable = True  # launches kernels only
+
+    def __init__(self, spec):
+        self.hidden, self.vocab = spec.hidden, spec.vocab
+        self.options = spec.frame_spec
+        self.final_norm = NORMS.build(spec.final_norm)
+
+    def param_shapes(self, tied):
+        shapes = {"embed": (self.vocab, self.hidden), "final_norm": tuple(self.final_norm.param_shapes()["weight"])}
+        if self.options.passes > 0:
+            shapes.update(loop_in=(self.hidden, 2 * self.hidden), loop_step=(self.options.passes, self.hidden))
+        if not tied:
+            shapes["head"] = (self.vocab, self.hidden)
+        return shapes
+
+    def bind(self, params, ctx):
+        self.ctx = ctx
+        self.table = to_device(params["embed"], ctx, ctx.dtype)
+        self.tied = "head" not in params
+        self.head = Linear(self.table if self.tied else to_device(params["head"], ctx, ctx.dtype))
+        self.final_norm.bind({"weight": params["final_norm"]}, ctx)
+        self.ones = torch.ones(1, dtype=torch.float32, device=ctx.device)
+        self.loop_in = self.loop_step = self.kept = None
+        if self.options.passes > 0:
+            self.loop_in = Linear(to_device(params["loop_in"], ctx, ctx.dtype))
+            self.loop_step = to_device(params["loop_step"], ctx, torch.float32)
+
+    def step_weights(self):
+        return [self.head.weight, *self.final_norm.step_weights(), self.loop_in.weight if self.loop_in else None, self.loop_step]
+
+    def embed(self, batch, ws, status):
+        n = batch.n_rows
+        x = ws.get("x_streams", (n, 1, self.hidden), torch.float32)
+        ops.embed(batch.tokens, self.table, x.view(n, self.hidden), status)
+        if self.loop_in is not None:
+            self.kept = ws.get("x_embedded", (n, self.hidden), torch.float32)
+            ops.embed(batch.tokens, self.table, self.kept, status)
+        return x
+
+    def inject(self, x, pending, batch, ws, t):
+        """The stream made anew before pass t; returns what is pending afterwards (nothing)."""
+        if self.loop_in is None or not 0 <= t < self.options.passes:
+            raise ValueError(f"the schedule starts pass {t}, but the frame has {self.options.passes} passes")
+        if pending is not None and (pending.mult != 1.0 or x.shape[1] != 1):
+            raise ValueError("the stream is made anew from one stream whose branches are added as they are")
+        n = batch.n_rows
+        beside = ws.get("x_beside", (n, 2 * self.hidden), self.ctx.dtype)
+        ops.stream_beside(x, pending.y if pending is not None else None, self.kept, beside, n)
+        self.loop_in.forward(beside, x.view(x.shape[0], self.hidden), n)
+        ops.add_vector(x, self.loop_step[t], n)
+        return None
+
+    def logits(self, x, pending, batch, ws):
+        from .streams import read_streams
+        r = batch.n_logit_rows
+        out = ws.get("logits", (max(r, 1), self.vocab), torch.float32)[:r]
+        if r:
+            xn = ws.get("xn_final", (r, self.hidden), self.ctx.dtype)
+            read_streams(x, pending, self.ones, self.final_norm, xn, rows=batch.logit_rows, n_rows=r)
+            self.head.forward(xn, out, r)
+        return out

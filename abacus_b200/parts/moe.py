@@ -33,8 +33,12 @@ class RoutedMLP:
         s = self.spec = spec
         if not 1 <= s.top <= s.experts + s.identity:
             raise ValueError(f"top {s.top} of {s.experts + s.identity} experts")
-        if s.score not in ("sigmoid", "softmax_chosen", "softmax_all"):
-            raise ValueError(f"router score {s.score!r} is none of sigmoid, softmax_chosen, softmax_all")
+        if s.score not in ("sigmoid", "softmax_chosen", "softmax_all", "table"):
+            raise ValueError(f"router score {s.score!r} is none of sigmoid, softmax_chosen, softmax_all, table")
+        self.by_table = s.score == "table"  # no router: a table names every token id's experts, each with weight 1 / top
+        if self.by_table and (s.identity or s.correction or s.shared is not None or s.weight_on != "output" or s.vocab < 1):
+            raise ValueError("experts picked by a table have their weight 1 / top on the outputs, a table of `vocab` rows "
+                             "and neither a shared expert, experts that return their input nor a correction")
         if s.identity < 0 or (s.identity and s.weight_on != "output"):
             raise ValueError("experts that return their input go with the weight on the experts' outputs")
         if (s.correction or s.weight_scale != 1.0) and s.score != "softmax_all":
@@ -42,7 +46,7 @@ class RoutedMLP:
         if s.top > s.experts + s.identity:
             raise ValueError(f"top {s.top} of {s.experts + s.identity} router outputs")
         # the weight applied in float32 where a token's pairs are summed (else on the row that enters the last product)
-        self.weighted_sum = s.weight_on == "output" and (s.identity > 0 or s.score == "softmax_all")
+        self.weighted_sum = s.weight_on == "output" and (s.identity > 0 or s.score in ("softmax_all", "table"))
         if self.weighted_sum and s.shared is not None:
             raise ValueError("a shared expert beside weights on the outputs is not built")
         self.gated = s.expert.activation == "silu_gated"
@@ -56,7 +60,7 @@ class RoutedMLP:
 
     def param_shapes(self):
         s = self.spec
-        shapes = {"router": (s.experts + s.identity, s.hidden)}
+        shapes = {"table": (s.vocab, s.top)} if self.by_table else {"router": (s.experts + s.identity, s.hidden)}
         if s.correction:
             shapes["correction"] = (s.experts + s.identity,)
         for e in range(s.experts):
@@ -70,7 +74,8 @@ class RoutedMLP:
 
     def bind(self, params, ctx):
         s, self.ctx = self.spec, ctx
-        self.router = to_device(params["router"], ctx, torch.float32)
+        self.router = None if self.by_table else to_device(params["router"], ctx, torch.float32)
+        self.table = to_device(params["table"], ctx, torch.int32) if self.by_table else None
         self.correction = to_device(params["correction"], ctx, torch.float32) if s.correction else None
         ups, downs = [params[f"up{e}"] for e in range(s.experts)], [params[f"down{e}"] for e in range(s.experts)]
         if self.gated:  # an expert's first matrix: its gate rows, then its up rows
@@ -103,9 +108,12 @@ class RoutedMLP:
         pairs = n * top
         expert = ws.get("moe_expert", (pairs,), torch.int32)
         weight = ws.get("moe_weight", (pairs,), torch.float32)
-        ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen",
-                      always=s.experts if self.stacked_shared else None, softmax_all=s.score == "softmax_all",
-                      correction=self.correction, weight_scale=s.weight_scale, n_real=s.experts)
+        if self.by_table:
+            ops.moe_table(batch, self.table, s.experts, s.top, expert, weight, ops.kernel_status(self.ctx.device)[:1])
+        else:
+            ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen",
+                          always=s.experts if self.stacked_shared else None, softmax_all=s.score == "softmax_all",
+                          correction=self.correction, weight_scale=s.weight_scale, n_real=s.experts)
         on_input = s.weight_on == "input"
         if self.weighted_sum:
             return self.forward_weighted_sum(xn, out, expert, weight, n, pairs, ws)
