@@ -95,7 +95,7 @@ def rotate(x, positions, rot, pairing):
     f, mag = frequencies(rot)
     angle = np.asarray(positions, dtype=np.float64)[:, None] * f[None, :]
     shape = (len(positions),) + (1,) * (x.ndim - 2) + (dims // 2,)
-    c, s = (np.cos(angle) * mag).reshape(shape), (np.sin(angle) * mag).reshape(shape)
+    c, s = (np.cos(angle) * mag).reshape(shape).astype(x.dtype), (np.sin(angle) * mag).reshape(shape).astype(x.dtype)
     out = x.copy()
     if pairing == "half":
         u, v = x[..., :dims // 2], x[..., dims // 2:dims]
@@ -129,8 +129,9 @@ def latent_attention(h, m, w, eps, state):
     q = (cq @ w["uq"].T).reshape(T, H, K + R)
     down = h @ w["dkv"].T
     c = rms_norm(down[:, :rank], w["dkv.norm"], eps)
-    r = rotate(down[:, rank:], positions, m["rot"], "half")
-    q_rot = rotate(q[:, :, K:], positions, m["rot"], "half")
+    r, q_rot = down[:, rank:], q[:, :, K:]
+    if m.get("rot"):
+        r, q_rot = rotate(r, positions, m["rot"], "half"), rotate(q_rot, positions, m["rot"], "half")
     if state is not None:
         c, r = np.concatenate([state[0], c]), np.concatenate([state[1], r])
     k = (c @ w["uk"].T).reshape(-1, H, K)
@@ -172,7 +173,7 @@ def wkv(h, m, w, eps, state):
     """state: (the token before [d], S [H, K, K])."""
     H, K = m["heads"], m["dim"]
     T, d = h.shape
-    before, S = (np.zeros(d), np.zeros((H, K, K))) if state is None else (state[0], state[1].copy())
+    before, S = (np.zeros(d, h.dtype), np.zeros((H, K, K), h.dtype)) if state is None else (state[0], state[1].copy())
     shifted = np.concatenate([before[None], h[:-1]])
     mix = {s: h + (shifted - h) * w["mu." + s] for s in "rkvgw"}
     r = (mix["r"] @ w["r"].T).reshape(T, H, K)
@@ -180,7 +181,7 @@ def wkv(h, m, w, eps, state):
     v = (mix["v"] @ w["v"].T).reshape(T, H, K)
     gate = silu(mix["g"] @ w["g"].T)
     decay = np.exp(-np.exp(np.tanh(mix["w"] @ w["w1"].T) @ w["w2"].T + w["w0"])).reshape(T, H, K)
-    o = np.zeros((T, H, K))
+    o = np.zeros((T, H, K), h.dtype)
     for t in range(T):
         kv = k[t][:, :, None] * v[t][:, None, :]
         o[t] = np.einsum("hk,hkv->hv", r[t], S + w["u"][:, :, None] * kv)
@@ -221,8 +222,10 @@ def part(weights, prefix):
 
 
 class PlainTilulorn:
-    def __init__(self, config, weights):
-        self.config, self.w = config, weights
+    def __init__(self, config, weights, real=np.float64):
+        """real: the type everything is computed in (float32: to see what float32 itself loses on an input)."""
+        self.config = config
+        self.w = {n: (t if t.dtype.kind == "i" else t.astype(real)) for n, t in weights.items()}
         self.eps = config["norm"]["eps"]
         self.order = run_order(config)
 
