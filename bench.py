@@ -521,6 +521,50 @@ def build_linonex(size):
     return model
 
 
+# Tilulorn at the same widths, depths and vocabulary: of every four layers the first is latent attention (heads of
+# 128 + 64 rotated, values of 128, 192 latents: a cache row of 256 elements a token for all heads; queries through a
+# latent of their own; blended frequencies; gated heads), the third attention whose values are its keys (heads of 128
+# over 8 key heads, a window of 1,024, a sink, slowed frequencies, gated heads), the second and fourth wkv time mixing
+# (heads of 64 x 64 state); every feed-forward 16 gated experts of which a table gives a token 2, each a quarter of the
+# dense size. The first four layers are one pass, so that the stream is made anew from itself and the embedding once.
+TILULORN_SIZES = {
+    "s": dict(heads=16, kv_heads=8, q_rank=384, wkv_heads=16, decay_rank=64, experts=16, top=2, expert_ff=768),
+    "m": dict(heads=32, kv_heads=8, q_rank=768, wkv_heads=40, decay_rank=64, experts=16, top=2, expert_ff=2432),
+}
+
+
+def build_tilulorn(size):
+    import torch
+    from abacus_b200.config import get_architecture
+    from abacus_b200.config.tilulorn import (TilulornConfig, TilulornExperts, TilulornLatent, TilulornLayer, TilulornLoop,
+                                             TilulornRotation, TilulornWindowed, TilulornWkv)
+    from abacus_b200.models import Model
+    from abacus_b200.weights import random_tensors
+    z, v = DESIGN_SIZES[size], TILULORN_SIZES[size]
+    mlp = TilulornExperts(v["experts"], v["top"], v["expert_ff"])
+    latent = TilulornLatent(v["heads"], 128, 64, 128, 192, v["q_rank"], 192 ** -0.5, TilulornRotation(10000.0, 64, 4.0, 4096, 32.0, 1.0))
+    windowed = TilulornWindowed(v["heads"], v["kv_heads"], 128, 128 ** -0.5, 1024, TilulornRotation(1000000.0, 128, 2.0, None, None, None))
+    wkv = TilulornWkv(v["wkv_heads"], 64, v["decay_rank"])
+    kinds = [("latent_attention", latent), ("wkv", wkv), ("attention", windowed), ("wkv", wkv)]
+    layers = tuple(TilulornLayer(*kinds[i % 4], mlp) for i in range(z["layers"]))
+    config = TilulornConfig(vocab=z["vocab"], width=z["width"], layers=layers, eps=1e-6, loop=TilulornLoop(0, 4, 1))
+    arch = get_architecture("Tilulorn")
+    spec = config.to_spec()
+    expected, _ = arch.tensor_names(spec, None)
+    device = torch.device("cuda", 0)
+    tables = {n: shape for n, shape in expected.items() if n.endswith(".mlp.table")}
+    tensors = random_tensors({n: shape for n, shape in expected.items() if n not in tables}, seed=5, std=0.02, device=device,
+                             rule=arch.random_moments)
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    for n, (rows, top) in tables.items():  # a token's experts: `top` in a row from a random first one, so they differ
+        first = torch.randint(0, v["experts"], (rows, 1), generator=gen)
+        tensors[n] = ((first + torch.arange(top)[None, :]) % v["experts"]).to(torch.int32)
+    model = Model(spec, arch.layout(spec), tensors, torch.bfloat16, device)
+    del tensors
+    torch.cuda.empty_cache()
+    return model
+
+
 def state_and_cache_bytes(model, tokens_held, n_seqs):
     """Bytes of keys, values and recurrent state a decode step moves for n_seqs sequences that hold tokens_held
     tokens together: a window's keys at most, the keys of the token's own chunk where attention sees no others, a state
@@ -562,7 +606,7 @@ def routed_expert_bytes(model, n_rows):
 
 
 def run_design(args):
-    """--design temetar | movarax | linonex: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3
+    """--design temetar | movarax | linonex | tilulorn: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3
     shape of equal size (--beside: beside another design of equal size instead)."""
     import torch
     from abacus_b200.kernels import build_all
@@ -575,6 +619,8 @@ def run_design(args):
         shape = {**{k: shape[k] for k in ("width", "ff", "layers", "vocab")}, **MOVARAX_SIZES[args.size]}
     if args.design == "linonex":
         shape = {**{k: shape[k] for k in ("width", "ff", "layers", "vocab")}, **LINONEX_SIZES[args.size]}
+    if args.design == "tilulorn":
+        shape = {**{k: shape[k] for k in ("width", "layers", "vocab")}, **TILULORN_SIZES[args.size]}
     out = {"design": args.design.capitalize(), "size": args.size, "shape": shape,
            "batch": args.batch, "prompt_tokens": PROMPT, "steps": args.steps, "warmup": args.warmup, "peaks": pk}
     for which in (args.design, args.beside):
@@ -584,6 +630,8 @@ def run_design(args):
             model = build_movarax(args.size)
         elif which == "linonex":
             model = build_linonex(args.size)
+        elif which == "tilulorn":
+            model = build_tilulorn(args.size)
         else:
             model, _ = build_model(z["qwen"])
         prompts = prompts_for(args.batch, model.spec.vocab, 10 + args.batch)
@@ -692,10 +740,10 @@ def main():
     ap.add_argument("--config", default="0.6b", choices=sorted(CONFIGS), help="whose workload the line reports")
     ap.add_argument("--skip-large", action="store_true", help="leave the 4b and 8b workloads out of `points`")
     ap.add_argument("--ragged", action="store_true", help="with --only prefill: the configuration's own prompts")
-    ap.add_argument("--design", default=None, choices=["temetar", "movarax", "linonex"],
+    ap.add_argument("--design", default=None, choices=["temetar", "movarax", "linonex", "tilulorn"],
                     help="instead of the default workload: this design at --size beside the Qwen3 shape of equal size")
     ap.add_argument("--size", default="s", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
-    ap.add_argument("--beside", default="qwen3", choices=["qwen3", "temetar", "movarax"],
+    ap.add_argument("--beside", default="qwen3", choices=["qwen3", "temetar", "movarax", "linonex"],
                     help="with --design: the model of equal size that runs beside it")
     args = ap.parse_args()
     if args.gpus != 1:
