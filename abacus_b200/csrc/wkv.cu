@@ -27,21 +27,74 @@ struct TokenShift {
     const int *token_seq, *seq_start, *seq_slot;
 };
 
+// A thread has one column (a CTA 128 of them: blockIdx.y counts the runs of columns), so that no load waits for a store.
 template <typename T> __global__ void __launch_bounds__(128) token_shift_kernel(TokenShift p) {
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, j = blockIdx.y * 128 + threadIdx.x;
     pdl_wait();
     const int seq = p.token_seq[t];
-    if (seq < 0) return;
+    if (seq < 0 || j >= p.d) return;
     const bool first = t == p.seq_start[seq];
     float *last = p.last + (long long)p.seq_slot[seq] * p.d;
     const T *x = (const T *)p.x + (long long)t * p.d;
     T *out = (T *)p.out + (long long)t * p.d;
-    for (int j = threadIdx.x; j < p.d; j += 128) {
-        const float h = to_float(x[j]);
-        const float before = first ? last[j] : to_float(x[j - p.d]);
-        const float diff = before - h;
-        for (int s = 0; s < p.blends; s++) out[s * p.plane + j] = from_float<T>(fmaf(diff, p.mu[(long long)s * p.d + j], h));
-        if (p.update) last[j] = h;  // (a step of one token a sequence: this row is the sequence's only one)
+    const float h = to_float(x[j]);
+    const float before = first ? last[j] : to_float(x[j - p.d]);
+    const float diff = before - h;
+    for (int s = 0; s < p.blends; s++) out[s * p.plane + j] = from_float<T>(fmaf(diff, __ldg(p.mu + (long long)s * p.d + j), h));
+    if (p.update) last[j] = h;  // (a step of one token a sequence: this row is the sequence's only one)
+}
+
+// The same for bfloat16 rows of a multiple of 8 columns and up to 8 blends: a thread has 8 consecutive columns, read
+// and written as 16-byte pieces, every load on its way before the first store.
+template <int BLENDS> __global__ void __launch_bounds__(128) token_shift_bf16x8_kernel(TokenShift p) {
+    const int t = blockIdx.x, j = (blockIdx.y * 128 + threadIdx.x) * 8;
+    pdl_wait();
+    const int seq = p.token_seq[t];
+    if (seq < 0 || j >= p.d) return;
+    const bool first = t == p.seq_start[seq];
+    float *last = p.last + (long long)p.seq_slot[seq] * p.d + j;
+    const __nv_bfloat16 *x = (const __nv_bfloat16 *)p.x + (long long)t * p.d + j;
+    const uint4 raw = *(const uint4 *)x;
+    float h[8], before[8];
+    const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&in[e]);
+        h[2 * e] = f.x, h[2 * e + 1] = f.y;
+    }
+    if (first) {
+        const float4 a = *(const float4 *)last, b = *(const float4 *)(last + 4);
+        before[0] = a.x, before[1] = a.y, before[2] = a.z, before[3] = a.w, before[4] = b.x, before[5] = b.y, before[6] = b.z, before[7] = b.w;
+    } else {
+        const uint4 r = *(const uint4 *)(x - p.d);
+        const uint32_t pw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&pw[e]);
+            before[2 * e] = f.x, before[2 * e + 1] = f.y;
+        }
+    }
+    float4 m[BLENDS][2];
+#pragma unroll
+    for (int s = 0; s < BLENDS; s++)
+        if (s < p.blends) m[s][0] = __ldg((const float4 *)(p.mu + (long long)s * p.d + j)), m[s][1] = __ldg((const float4 *)(p.mu + (long long)s * p.d + j + 4));
+    __nv_bfloat16 *out = (__nv_bfloat16 *)p.out + (long long)t * p.d + j;
+#pragma unroll
+    for (int s = 0; s < BLENDS; s++) {
+        if (s >= p.blends) break;
+        const float mu[8] = {m[s][0].x, m[s][0].y, m[s][0].z, m[s][0].w, m[s][1].x, m[s][1].y, m[s][1].z, m[s][1].w};
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(fmaf(before[2 * e] - h[2 * e], mu[2 * e], h[2 * e]),
+                                                            fmaf(before[2 * e + 1] - h[2 * e + 1], mu[2 * e + 1], h[2 * e + 1]));
+            w[e] = *(const uint32_t *)&h2;
+        }
+        *(uint4 *)(out + s * p.plane) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (p.update) {
+        *(float4 *)last = make_float4(h[0], h[1], h[2], h[3]);
+        *(float4 *)(last + 4) = make_float4(h[4], h[5], h[6], h[7]);
     }
 }
 
@@ -66,8 +119,10 @@ extern "C" int abk_token_shift(const void *x, int dtype, int n_tokens, int d, co
     p.x = x, p.last = last, p.mu = mu, p.out = out, p.plane = plane, p.d = d, p.blends = blends, p.update = update;
     p.token_seq = token_seq, p.seq_start = seq_start, p.seq_slot = seq_slot;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == ABK_BF16) abk_launch(token_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, p);
-    else abk_launch(token_shift_kernel<float>, dim3(n_tokens), dim3(128), 0, s, p);
+    if (dtype == ABK_BF16 && d % 8 == 0 && blends <= 8 && plane % 8 == 0 && ((uintptr_t)x | (uintptr_t)out | (uintptr_t)mu | (uintptr_t)last) % 16 == 0)
+        abk_launch(token_shift_bf16x8_kernel<8>, dim3(n_tokens, (d / 8 + 127) / 128), dim3(128), 0, s, p);
+    else if (dtype == ABK_BF16) abk_launch(token_shift_kernel<__nv_bfloat16>, dim3(n_tokens, (d + 127) / 128), dim3(128), 0, s, p);
+    else abk_launch(token_shift_kernel<float>, dim3(n_tokens, (d + 127) / 128), dim3(128), 0, s, p);
     return ABK_LAUNCH_RESULT();
 }
 
@@ -111,7 +166,29 @@ struct WkvScan {
     float *state;        // [slots][heads][dim][dim] (key, value)
     float *out;          // [tokens][heads * dim]
     const int *seq_start, *seq_slot;
+    // A step of prompts runs in segments of `chunk` tokens, all at once (blockIdx.z counts the step's segments, sequence
+    // after sequence): phase 1 walks each segment from an empty state and leaves its sum and the product of its decays,
+    // wkv_segment_prefix turns the sums into the states at the segments' starts (and leaves the last in the slot), phase 2
+    // walks each segment again from its start state for the outputs. chunk 0 (phase 0): a CTA walks a whole sequence.
+    int chunk, phase, n_seqs;
+    float *sums;         // [segments][heads][dim][dim]
+    float *prods;        // [segments][heads][dim]
 };
+
+// The segment blockIdx.z names: its sequence, its first row and its rows (0: none). Sequences are walked in order.
+__device__ __forceinline__ void wkv_segment(const int *seq_start, int n_seqs, int chunk, int z, int &seq, int &row0, int &n) {
+    n = 0;
+    int first = 0;
+    for (seq = 0; seq < n_seqs; seq++) {
+        const int start = seq_start[seq], len = seq_start[seq + 1] - start, count = (len + chunk - 1) / chunk;
+        if (z < first + count) {
+            const int c = z - first;
+            row0 = start + c * chunk, n = len - c * chunk < chunk ? len - c * chunk : chunk;
+            return;
+        }
+        first += count;
+    }
+}
 
 // N tokens of one thread's share: r, k, w point at the thread's channels of the first token (tokens `pitch` floats
 // apart), v at its column's value (tokens `v_pitch` apart); the column's output goes to out if `writes`.
@@ -160,7 +237,7 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
     constexpr int PER_V = (TOK * COLS + THREADS - 1) / THREADS;
     __shared__ __align__(16) float r_s[TOK][PITCH], k_s[TOK][PITCH], w_s[TOK][PITCH];
     __shared__ float v_s[TOK][COLS];
-    const int tile = blockIdx.x, h = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x, part = tid % PARTS, vc = tid / PARTS;
+    const int tile = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, part = tid % PARTS, vc = tid / PARTS;
     const int col = tile * COLS + vc;
     float u[DPT];
 #pragma unroll
@@ -169,18 +246,29 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
         u[i] = d < p.dim ? p.bonus[(long long)h * p.dim + d] : 0.0f;
     }
     pdl_wait();
-    const int row0 = p.seq_start[seq], n = p.seq_start[seq + 1] - row0;
+    int seq = blockIdx.z, row0, n;
+    if (p.chunk > 0) wkv_segment(p.seq_start, p.n_seqs, p.chunk, blockIdx.z, seq, row0, n);
+    else row0 = p.seq_start[seq], n = p.seq_start[seq + 1] - row0;
     if (n <= 0) return;  // (a sequence of the step's padding: its slot is someone else's)
-    float *state = p.state + ((long long)p.seq_slot[seq] * p.n_heads + h) * p.dim * p.dim;
+    float *state = p.phase == 0 ? p.state + ((long long)p.seq_slot[seq] * p.n_heads + h) * p.dim * p.dim
+                                : p.sums + ((long long)blockIdx.z * p.n_heads + h) * p.dim * p.dim;
     float s[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; i++) {
         const int d = part * DPT + i;
-        s[i] = d < p.dim && col < p.dim ? state[(long long)d * p.dim + col] : 0.0f;
+        s[i] = p.phase != 1 && d < p.dim && col < p.dim ? state[(long long)d * p.dim + col] : 0.0f;
     }
+    float decayed = 1.0f;  // phase 1: the product of this thread's staged decays (one channel, its share of the tokens)
     const T *proj = (const T *)p.proj;
     const long long hk = (long long)p.n_heads * p.dim;
-    float rr[PER], rk[PER], rw[PER], rv[PER_V];
+    // A chunk's rows are asked for a chunk ahead and kept as they come: nothing is done to a loaded value before the
+    // chunk is staged (an instruction that needs it would hold the warp until the load is back), so the loads' way from
+    // memory lies under the chunk before. A thread stages one channel (THREADS is a multiple of the padded channels).
+    static_assert(THREADS % DP == 0, "a thread stages one channel");
+    T rr[PER], rk[PER], rv[PER_V];
+    float rz[PER];
+    const int my_d = tid % DP, my_ch = h * p.dim + (my_d < p.dim ? my_d : 0);
+    const float my_w0 = p.w0[my_ch];
     auto fetch = [&](int c0) {
         const int cnt = n - c0 < TOK ? n - c0 : TOK;
 #pragma unroll
@@ -188,22 +276,16 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
             // (every load is made, from a place that exists, and dropped where it is not wanted: loads that hang on no
             // branch are all in flight together)
             if (it * THREADS >= cnt * DP) break;  // (the same for every thread: the chunk has no such token)
-            const int e = tid + it * THREADS, tok = e / DP, d = e % DP;
-            const bool in = tok < cnt && d < p.dim;
+            const int tok = (tid + it * THREADS) / DP;
             const long long row = row0 + c0 + (tok < cnt ? tok : cnt - 1);
-            const int ch = h * p.dim + (d < p.dim ? d : 0);
-            const T *r = proj + row * p.ld + ch;
-            const float rv_ = to_float(r[p.r_at]), kv_ = to_float(r[p.k_at]);
-            const float z = p.pre[row * hk + ch] + p.w0[ch];
-            rr[it] = in ? rv_ : 0.0f, rk[it] = in ? kv_ : 0.0f, rw[it] = in ? z : 0.0f;
+            const T *r = proj + row * p.ld + my_ch;
+            rr[it] = r[p.r_at], rk[it] = r[p.k_at], rz[it] = p.pre[row * hk + my_ch];
         }
 #pragma unroll
         for (int it = 0; it < PER_V; it++) {
             if (it * THREADS >= cnt * COLS) break;
             const int e = tid + it * THREADS, tok = e / COLS, c = tile * COLS + e % COLS;
-            const float v = to_float(proj[(long long)(row0 + c0 + (tok < cnt ? tok : cnt - 1)) * p.ld + p.v_at + (long long)h * p.dim +
-                                          (c < p.dim ? c : 0)]);
-            rv[it] = tok < cnt && c < p.dim ? v : 0.0f;
+            rv[it] = proj[(long long)(row0 + c0 + (tok < cnt ? tok : cnt - 1)) * p.ld + p.v_at + (long long)h * p.dim + (c < p.dim ? c : 0)];
         }
     };
     fetch(0);
@@ -213,13 +295,16 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
 #pragma unroll
         for (int it = 0; it < PER; it++) {
             if (it * THREADS >= cnt * DP) break;
-            const int e = tid + it * THREADS, tok = e / DP, d = e % DP, at = (d / DPT) * (DPT + 4) + d % DPT;
-            r_s[tok][at] = rr[it], k_s[tok][at] = rk[it], w_s[tok][at] = expf(-expf(rw[it]));
+            const int tok = (tid + it * THREADS) / DP, at = (my_d / DPT) * (DPT + 4) + my_d % DPT;
+            const bool in = tok < cnt && my_d < p.dim;
+            const float w = expf(-expf(rz[it] + my_w0));
+            r_s[tok][at] = in ? to_float(rr[it]) : 0.0f, k_s[tok][at] = in ? to_float(rk[it]) : 0.0f, w_s[tok][at] = w;
+            if (in) decayed *= w;
         }
 #pragma unroll
         for (int it = 0; it < PER_V; it++) {
             const int e = tid + it * THREADS;
-            if (e < cnt * COLS) v_s[e / COLS][e % COLS] = rv[it];
+            if (e < cnt * COLS) v_s[e / COLS][e % COLS] = tile * COLS + e % COLS < p.dim ? to_float(rv[it]) : 0.0f;
         }
         __syncthreads();
         if (c0 + TOK < n) fetch(c0 + TOK);
@@ -227,32 +312,80 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
         // multiply-adds follow one another
         const int at = part * (DPT + 4);
         float *out = p.out + (long long)(row0 + c0) * hk + (long long)h * p.dim + col;
-        const bool writes = part == 0 && col < p.dim;
+        const bool writes = part == 0 && col < p.dim && p.phase != 1;
         int tok = 0;
         for (; tok + 4 <= cnt; tok += 4)
             wkv_tokens<DPT, PARTS, 4>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
         for (; tok < cnt; tok++)
             wkv_tokens<DPT, PARTS, 1>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
     }
+    if (p.phase == 2) return;  // (the states between segments are wkv_segment_prefix's)
 #pragma unroll
     for (int i = 0; i < DPT; i++) {
         const int d = part * DPT + i;
         if (d < p.dim && col < p.dim) state[(long long)d * p.dim + col] = s[i];
     }
+    if (p.phase == 1 && tile == 0) {
+        // every thread staged the decays of one channel: the shares of a channel meet through shared memory
+        __syncthreads();
+        float *share = &r_s[0][0];
+        share[tid] = decayed;
+        __syncthreads();
+        if (tid < DP && tid < p.dim) {
+            float all = 1.0f;
+            for (int o = tid; o < THREADS; o += DP) all *= share[o];
+            p.prods[((long long)blockIdx.z * p.n_heads + h) * p.dim + tid] = all;
+        }
+    }
+}
+
+// The states at the segments' starts from the segments' own sums: along a sequence S <- prod * S + sum, the state before
+// each segment left where its sum was, the last in the sequence's slot. A thread an element of the state; four segments'
+// loads are on their way together.
+__global__ void __launch_bounds__(256) wkv_segment_prefix_kernel(float *sums, const float *prods, float *state, const int *seq_start,
+                                                                 const int *seq_slot, int n_heads, int dim, int chunk) {
+    const int e = blockIdx.x * 256 + threadIdx.x, h = blockIdx.y, seq = blockIdx.z;
+    pdl_wait();
+    const int len = seq_start[seq + 1] - seq_start[seq];
+    if (len <= 0 || e >= dim * dim) return;
+    int first = 0;
+    for (int q = 0; q < seq; q++) first += (seq_start[q + 1] - seq_start[q] + chunk - 1) / chunk;
+    const int count = (len + chunk - 1) / chunk, d = e / dim;
+    float *slot = state + ((long long)seq_slot[seq] * n_heads + h) * dim * dim + e;
+    float S = *slot;
+    for (int c0 = 0; c0 < count; c0 += 4) {
+        float u[4], pr[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const long long at = (long long)(first + (c0 + i < count ? c0 + i : count - 1)) * n_heads + h;
+            u[i] = sums[at * dim * dim + e], pr[i] = prods[at * dim + d];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (c0 + i >= count) break;
+            sums[((long long)(first + c0 + i) * n_heads + h) * dim * dim + e] = S;
+            S = fmaf(pr[i], S, u[i]);
+        }
+    }
+    *slot = S;
 }
 
 extern "C" int abk_wkv_scan(const void *proj, long long ld, int dtype, int r_at, int k_at, int v_at, int n_heads, int dim,
                             const float *pre, const float *w0, const float *bonus, float *state, float *out,
-                            const int *seq_start, const int *seq_slot, int n_seqs, void *stream) {
+                            const int *seq_start, const int *seq_slot, int n_seqs, int chunk, int segments, float *sums,
+                            float *prods, void *stream) {
     if (n_seqs <= 0) return 0;
     if (dim < 1 || dim > 256) ABK_REFUSE("wkv_scan: %d key channels a head are not 1 to 256", dim);
     if (n_heads < 1 || n_heads > 65535 || n_seqs > 65535) ABK_REFUSE("wkv_scan: %d heads, %d sequences", n_heads, n_seqs);
     WkvScan p;
     p.proj = proj, p.ld = ld, p.r_at = r_at, p.k_at = k_at, p.v_at = v_at, p.n_heads = n_heads, p.dim = dim;
     p.pre = pre, p.w0 = w0, p.bonus = bonus, p.state = state, p.out = out, p.seq_start = seq_start, p.seq_slot = seq_slot;
+    p.chunk = chunk, p.phase = 0, p.n_seqs = n_seqs, p.sums = sums, p.prods = prods;
+    if (chunk < 0 || (chunk > 0 && (segments < 1 || segments > 65535 || !sums || !prods)))
+        ABK_REFUSE("wkv_scan: %d segments of %d tokens", segments, chunk);
     cudaStream_t s = (cudaStream_t)stream;
     const int cols = dim <= 32 ? 32 : 16;  // value columns a CTA has
-    dim3 grid((dim + cols - 1) / cols, n_heads, n_seqs);
+    dim3 grid((dim + cols - 1) / cols, n_heads, chunk > 0 ? segments : n_seqs);
 #define WS_LAUNCH(T)                                                                                  \
     do {                                                                                              \
         if (dim <= 16) abk_launch(wkv_scan_kernel<T, 4, 4, 32, 16>, grid, dim3(128), 0, s, p);        \
@@ -261,6 +394,18 @@ extern "C" int abk_wkv_scan(const void *proj, long long ld, int dtype, int r_at,
         else if (dim <= 128) abk_launch(wkv_scan_kernel<T, 8, 16, 16, 16>, grid, dim3(256), 0, s, p); \
         else abk_launch(wkv_scan_kernel<T, 16, 16, 16, 8>, grid, dim3(256), 0, s, p);                 \
     } while (0)
+    if (chunk > 0) {  // the segments' sums, the states between them, the segments' outputs
+        p.phase = 1;
+        if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16);
+        else WS_LAUNCH(float);
+        int rc = ABK_LAUNCH_RESULT();
+        if (rc) return rc;
+        abk_launch(wkv_segment_prefix_kernel, dim3((dim * dim + 255) / 256, n_heads, n_seqs), dim3(256), 0, s, sums, prods, state,
+                   seq_start, seq_slot, n_heads, dim, chunk);
+        rc = ABK_LAUNCH_RESULT();
+        if (rc) return rc;
+        p.phase = 2;
+    }
     if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16);
     else WS_LAUNCH(float);
 #undef WS_LAUNCH

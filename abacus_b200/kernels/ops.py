@@ -1345,11 +1345,19 @@ def tanh_rows(src, dst, n):
     _check(lib, lib.abk_tanh_rows(_p(src), _p(dst), _i(_dt(dst)), _ll(n * src.shape[1]), _stream()), "tanh_rows")
 
 
-def wkv_scan(proj, r_at, k_at, v_at, n_heads, dim, pre, w0, bonus, state, out, batch):
+WKV_SEGMENT = 64        # tokens of a segment of the form for prompts
+WKV_SEGMENTS_FROM = 128  # rows of a step (one that is no decode step) from which its sequences are walked in segments
+
+
+def wkv_scan(proj, r_at, k_at, v_at, n_heads, dim, pre, w0, bonus, state, out, batch, ws=None):
     """The recurrence of a wkv layer for every sequence of the step and every head, float32:
         o = (S + diag(bonus) k v^T)^T r;    S <- diag(exp(-exp(pre + w0))) S + k v^T
     proj [tokens, .] as stored: r, k, v of head h at columns r_at / k_at / v_at + h * dim; pre float32 [tokens, heads * dim];
-    w0, bonus float32 [heads * dim]; state float32 [slots, heads, dim, dim] (key, value); out float32 [tokens, heads * dim]."""
+    w0, bonus float32 [heads * dim]; state float32 [slots, heads, dim, dim] (key, value); out float32 [tokens, heads * dim].
+    A decode step, or a small one, walks each sequence token by token. A step of prompts (with ws, a Workspace) walks all
+    segments of WKV_SEGMENT tokens at once, twice: for each segment's own sum from an empty state, and, once the states
+    between the segments are made from the sums, for the outputs (the same numbers, summed in another order). Which way a
+    step goes depends on its rows and sequences alone, not on how long each sequence is."""
     _need_cuda(proj, pre, w0, bonus, state, out)
     lib = load_module("wkv")
     hk = n_heads * dim
@@ -1357,9 +1365,20 @@ def wkv_scan(proj, r_at, k_at, v_at, n_heads, dim, pre, w0, bonus, state, out, b
     assert pre.is_contiguous() and out.is_contiguous() and state.is_contiguous() and pre.shape[1] == out.shape[1] == hk
     assert w0.numel() == bonus.numel() == hk and state.shape[1:] == (n_heads, dim, dim)
     assert proj.shape[1] >= max(r_at, k_at, v_at) + hk
+    n_seqs = batch.seq_slot.numel()
+    chunk, segments, sums, prods = 0, 0, None, None
+    if ws is not None and not batch.is_decode and batch.n_rows >= WKV_SEGMENTS_FROM:
+        chunk = WKV_SEGMENT
+        segments = -(-batch.n_rows // chunk) + n_seqs  # (at most: every sequence's last segment may be a short one)
+        if segments <= 65535:
+            sums = ws.get("wkv_sums", (segments, n_heads, dim, dim), torch.float32)
+            prods = ws.get("wkv_prods", (segments, n_heads, dim), torch.float32)
+        else:
+            chunk = segments = 0
     _check(lib, lib.abk_wkv_scan(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(r_at), _i(k_at), _i(v_at), _i(n_heads), _i(dim),
                                  _p(pre), _p(w0), _p(bonus), _p(state), _p(out), _p(batch.seq_start), _p(batch.seq_slot),
-                                 _i(batch.seq_slot.numel()), _stream()), "wkv_scan")
+                                 _i(n_seqs), _i(chunk), _i(segments), _p(sums), _p(prods), _stream()), "wkv_scan",
+           kernels=3 if chunk else 1)
 
 
 # ------------------------------------------------------------------ experts by a table (csrc/moe.cu)

@@ -112,7 +112,7 @@ class Attention:
         self.ctx = ctx
         wqkv = torch.cat([params["wq"], params["wk"]] + ([params["wv"]] if "wv" in params else []), dim=0)
         if self.proj_row > wqkv.shape[0]:
-            wqkv = torch.cat([wqkv, torch.zeros((self.proj_row - wqkv.shape[0], wqkv.shape[1]), dtype=wqkv.dtype)], dim=0)
+            wqkv = torch.cat([wqkv, torch.zeros((self.proj_row - wqkv.shape[0], wqkv.shape[1]), dtype=wqkv.dtype, device=wqkv.device)], dim=0)
         if self.spec.head_gate:
             wqkv[self.gate_at:self.gate_at + self.spec.n_heads] = params["wg"]
         self.qkv_proj = Linear(to_device(wqkv, ctx, ctx.dtype))

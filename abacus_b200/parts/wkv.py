@@ -92,7 +92,7 @@ class Wkv:
         self.w2.forward(inner, pre, n)
         o = ws.get("wkv_o", (n, self.size), torch.float32)
         ops.wkv_scan(proj, self.at["r"], self.at["k"], self.at["v"], s.n_heads, s.key_dim, pre, self.w0, self.bonus,
-                     cache.states["wkv_state"], o, batch)
+                     cache.states["wkv_state"], o, batch, ws=ws)
         normed = ws.get("wkv_normed", (n, self.size), dt)
         ops.gated_head_norm(o, proj[:, self.at["g"]:self.at["g"] + self.size], self.out_norm, normed, n, s.n_heads, s.key_dim,
                             s.norm_eps, silu=True)
