@@ -564,34 +564,66 @@ struct QkvWhole {
     const int *token_seq, *token_pos, *seq_slot, *seq_len_after;
 };
 
-template <typename T> __global__ void __launch_bounds__(256) qkv_prep_whole_kernel(QkvWhole p) {
-    extern __shared__ float whole[];  // the token's q and k, float32
+// VEC elements at a time: 8 for bfloat16 rows whose heads are a multiple of 8 (16-byte pieces), else 1.
+template <typename T, int VEC> __device__ __forceinline__ void whole_load(const T *p, float *f) {
+    if constexpr (VEC == 8) {
+        const uint4 raw = *(const uint4 *)p;
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 v = __bfloat1622float2(*(const __nv_bfloat162 *)&w[k]);
+            f[2 * k] = v.x, f[2 * k + 1] = v.y;
+        }
+    } else {
+        f[0] = to_float(*p);
+    }
+}
+template <typename T, int VEC> __device__ __forceinline__ void whole_store(T *p, T *q, const float *f) {  // q: a second place, or null
+    if constexpr (VEC == 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+            w[k] = *(const uint32_t *)&h2;
+        }
+        *(uint4 *)p = make_uint4(w[0], w[1], w[2], w[3]);
+        if (q) *(uint4 *)q = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        *p = from_float<T>(f[0]);
+        if (q) *q = *p;
+    }
+}
+
+template <typename T, int VEC> __global__ void __launch_bounds__(256) qkv_prep_whole_kernel(QkvWhole p) {
+    extern __shared__ __align__(16) float whole[];  // the token's q and k, float32
     __shared__ float scratch[33];
     const int t = blockIdx.x, tid = threadIdx.x;
+    const int hd = p.head_dim, q_size = p.n_heads * hd, k_size = p.n_kv_heads * hd;
     pdl_wait();
     const int seq = p.token_seq[t];
     if (seq < 0) return;
-    const int pos = p.token_pos[t], hd = p.head_dim;
-    const int q_size = p.n_heads * hd, k_size = p.n_kv_heads * hd;
+    const int pos = p.token_pos[t];
     const T *src = (const T *)p.src + (long long)t * p.lds;
     T *dst = (T *)p.dst + (long long)t * p.ldd;
+    const bool keeps = p.k_pool && cache_keeps(p.cache, pos, p.seq_len_after[seq]);
+    const int page = keeps ? cache_page(p.cache, p.seq_slot[seq], pos) : 0;
     float sq = 0.0f, sk = 0.0f;
-    for (int j = tid; j < q_size + k_size; j += 256) {
-        const float v = to_float(src[j]);
-        whole[j] = v;
-        if (j < q_size) sq = fmaf(v, v, sq);
-        else sk = fmaf(v, v, sk);
+    for (int j = tid * VEC; j < q_size + k_size; j += 256 * VEC) {
+        float f[VEC];
+        whole_load<T, VEC>(src + j, f);
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) whole[j + e] = f[e], ss = fmaf(f[e], f[e], ss);
+        if (j < q_size) sq += ss;
+        else {  // a key as projected is its value: to the row and to the cache as it is
+            sk += ss;
+            const int jk = j - q_size;
+            whole_store<T, VEC>(dst + q_size + k_size + jk,
+                                keeps ? (T *)p.v_pool + cache_offset(p.cache, page, jk / hd, p.n_kv_heads, pos, hd) + jk % hd : nullptr, f);
+        }
     }
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
-    const bool keeps = p.k_pool && cache_keeps(p.cache, pos, p.seq_len_after[seq]);
-    const int page = keeps ? cache_page(p.cache, p.seq_slot[seq], pos) : 0;
-    // the values: the keys as they were projected
-    for (int j = tid; j < k_size; j += 256) {
-        const T v = src[q_size + j];
-        dst[q_size + k_size + j] = v;
-        if (keeps) ((T *)p.v_pool)[cache_offset(p.cache, page, j / hd, p.n_kv_heads, pos, hd) + j % hd] = v;
-    }
     if (p.q_norm) {
         const float rq = 1.0f / sqrtf(sq / (float)q_size + p.eps), rk = 1.0f / sqrtf(sk / (float)k_size + p.eps);
         for (int j = tid; j < q_size + k_size; j += 256)
@@ -610,13 +642,10 @@ template <typename T> __global__ void __launch_bounds__(256) qkv_prep_whole_kern
         }
         __syncthreads();
     }
-    for (int j = tid; j < q_size + k_size; j += 256) {
-        const T v = from_float<T>(whole[j]);
-        dst[j] = v;
-        if (keeps && j >= q_size) {
-            const int jk = j - q_size;
-            ((T *)p.k_pool)[cache_offset(p.cache, page, jk / hd, p.n_kv_heads, pos, hd) + jk % hd] = v;
-        }
+    for (int j = tid * VEC; j < q_size + k_size; j += 256 * VEC) {
+        const int jk = j - q_size;
+        whole_store<T, VEC>(dst + j, keeps && jk >= 0 ? (T *)p.k_pool + cache_offset(p.cache, page, jk / hd, p.n_kv_heads, pos, hd) + jk % hd
+                                                       : nullptr, whole + j);
     }
 }
 
@@ -640,19 +669,20 @@ extern "C" int abk_qkv_prep_whole(const void *src, long long lds, void *dst, lon
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
     p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_len_after = seq_len_after;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == ABK_BF16) {
-        if (smem > 48 * 1024) {
-            cudaError_t e = abk_allow_shared_memory((const void *)qkv_prep_whole_kernel<__nv_bfloat16>, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        abk_launch(qkv_prep_whole_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, s, p);
-    } else {
-        if (smem > 48 * 1024) {
-            cudaError_t e = abk_allow_shared_memory((const void *)qkv_prep_whole_kernel<float>, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        abk_launch(qkv_prep_whole_kernel<float>, dim3(n_tokens), dim3(256), smem, s, p);
-    }
+    const bool pieces = dtype == ABK_BF16 && head_dim % 8 == 0 && lds % 8 == 0 && ldd % 8 == 0 &&
+                        ((uintptr_t)src | (uintptr_t)dst | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16 == 0;
+#define WHOLE_LAUNCH(KERNEL)                                                            \
+    do {                                                                                \
+        if (smem > 48 * 1024) {                                                         \
+            cudaError_t e = abk_allow_shared_memory((const void *)KERNEL, (int)smem);   \
+            if (e != cudaSuccess) return (int)e;                                        \
+        }                                                                               \
+        abk_launch(KERNEL, dim3(n_tokens), dim3(256), smem, s, p);                      \
+    } while (0)
+    if (pieces) WHOLE_LAUNCH((qkv_prep_whole_kernel<__nv_bfloat16, 8>));
+    else if (dtype == ABK_BF16) WHOLE_LAUNCH((qkv_prep_whole_kernel<__nv_bfloat16, 1>));
+    else WHOLE_LAUNCH((qkv_prep_whole_kernel<float, 1>));
+#undef WHOLE_LAUNCH
     return ABK_LAUNCH_RESULT();
 }
 
@@ -671,10 +701,36 @@ __global__ void __launch_bounds__(256) gate_heads_kernel(T *x, long long ldx, co
     *at = from_float<T>(to_float(*at) * g);
 }
 
+// The same for bfloat16 heads of a multiple of 8 elements: a thread has 8 consecutive elements, one 16-byte piece.
+__global__ void __launch_bounds__(256) gate_heads_bf16x8_kernel(__nv_bfloat16 *x, long long ldx, const __nv_bfloat16 *gate, long long ldg,
+                                                                int heads, int size, long long groups) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= groups) return;
+    const long long per = (long long)heads * size / 8, t = i / per;
+    const int e = (int)(i - t * per) * 8;
+    const float g = 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ldg + e / size])));
+    uint4 *at = (uint4 *)(x + t * ldx + e);
+    uint4 raw = *at;
+    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float2 f = __bfloat1622float2(*(const __nv_bfloat162 *)&w[k]);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(f.x * g, f.y * g);
+        w[k] = *(const uint32_t *)&h2;
+    }
+    *at = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 extern "C" int abk_gate_heads(void *x, long long ldx, const void *gate, long long ldg, int dtype, int n_tokens, int heads, int size,
                               void *stream) {
     const long long total = (long long)n_tokens * heads * size;
     if (total <= 0) return 0;
+    if (dtype == ABK_BF16 && size % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && total / 8 + 255 < 0x7fffffffLL * 256) {
+        abk_launch(gate_heads_bf16x8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                   (__nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)gate, ldg, heads, size, total / 8);
+        return ABK_LAUNCH_RESULT();
+    }
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) ABK_REFUSE("gate_heads: %lld elements are more than a grid takes", total);
     cudaStream_t s = (cudaStream_t)stream;

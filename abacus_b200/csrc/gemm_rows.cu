@@ -55,7 +55,7 @@ template <int NT, int TILE, bool GATED, typename TO>
 __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
                                                                  const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
                                                                  int M, int N, int K, long long ldx, long long ldw,
-                                                                 long long ldo, int block) {
+                                                                 long long ldo, int block, long long x_plane) {
     __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     const int ranks = (int)tc::cluster_size(), rank = (int)tc::cluster_rank();  // the cluster splits K
@@ -64,7 +64,9 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
     // (a turn of gate rows is a multiple of 8 long, so a CTA's 8 outputs lie in one turn)
     const long long w_row = GATED ? (long long)(n0 / block) * 2 * block + n0 % block + r : n0 + r;
     const __nv_bfloat16 *w_lo = w + w_row * ldw + 8 * c, *w_hi = w_lo + (GATED ? (long long)block : 8) * ldw;
-    const __nv_bfloat16 *x0 = x + (long long)r * ldx + 8 * c;  // token r of tile t is 8 t rows further
+    // (not GATED, block > 0: the output features come in runs of `block`, and run i reads x + i * x_plane: several
+    // products of one shape of rows, each with an input of its own, in one launch)
+    const __nv_bfloat16 *x0 = x + (!GATED && block > 0 ? (long long)(n0 / block) * x_plane : 0) + (long long)r * ldx + 8 * c;  // token r of tile t is 8 t rows further
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
@@ -166,10 +168,12 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
 }
 
 // x [M, K], w [N, K] bfloat16 (row pitches ldx, ldw in elements); out [M, N] bfloat16 or float32.
-// M <= 16, K a multiple of 32, rows 16-byte aligned.
-extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
-                             long long ldw, long long ldo, void *stream) {
+// M <= 16, K a multiple of 32, rows 16-byte aligned. block > 0: output features [i * block, (i + 1) * block) read
+// x + i * x_plane (block a multiple of 16; the last run may be shorter).
+static int gemm_rows_launch(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
+                            long long ldw, long long ldo, int block, long long x_plane, void *stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (block < 0 || block % 16 || x_plane % 8) ABK_REFUSE("gemm_rows: runs of %d features, inputs %lld elements apart", block, x_plane);
     if (M > 64) ABK_REFUSE("gemm_rows: %d rows are more than 64", M);
     if (K <= 0 || K % 32 || ldx % 8 || ldw % 8) ABK_REFUSE("gemm_rows: K = %d must be a multiple of 32 and the pitches of 8", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) ABK_REFUSE("gemm_rows: operands must be 16-byte aligned");
@@ -186,7 +190,7 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define ROWS_LAUNCH(NT, TILE, TO)                                                                                     \
     abk_launch_clusters(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, ranks, xb, wb, (TO *)out, M, \
-                        N, K, ldx, ldw, ldo, 0)
+                        N, K, ldx, ldw, ldo, block, x_plane)
 #define ROWS_BY_M(TO)                                                                     \
     if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, TO); else ROWS_LAUNCH(1, 16, TO); }       \
     else if (M <= 16) { if (narrow) ROWS_LAUNCH(2, 8, TO); else ROWS_LAUNCH(2, 16, TO); } \
@@ -196,6 +200,19 @@ extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dt
 #undef ROWS_BY_M
 #undef ROWS_LAUNCH
     return ABK_LAUNCH_RESULT();
+}
+
+extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
+                             long long ldw, long long ldo, void *stream) {
+    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, 0, 0, stream);
+}
+
+// Several products of one launch: out[:, i * block : (i + 1) * block] = x_i . w[i * block : (i + 1) * block]^T with
+// x_i = x + i * x_plane (each [M, K] with pitch ldx).
+extern "C" int abk_gemm_rows_planes(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
+                                    long long ldw, long long ldo, int block, long long x_plane, void *stream) {
+    if (block <= 0) ABK_REFUSE("gemm_rows_planes: runs of %d features", block);
+    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, block, x_plane, stream);
 }
 
 // act[M, N] = silu(x . w_gate^T) * (x . w_up^T) where w [2 N, K] holds gate and up rows in turns of `block`
@@ -212,7 +229,7 @@ extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define GATED_LAUNCH(NT) \
-    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo, block)
+    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo, block, 0LL)
     if (M <= 8) GATED_LAUNCH(1);
     else if (M <= 16) GATED_LAUNCH(2);
     else if (M <= 32) GATED_LAUNCH(4);

@@ -138,19 +138,33 @@ extern "C" int abk_token_shift_keep(const void *x, int dtype, int d, float *last
 }
 
 // ---------------------------------------------------------------- the activation inside the decay's pair of matrices
-// dst = tanh(src): src float32 (the first product's sums), dst as stored (the second product's input).
-template <typename T> __global__ void __launch_bounds__(256) tanh_rows_kernel(const float *src, T *dst, long long total) {
+// dst = tanh(src) over `cols` columns of n rows (rows of any pitch): src float32 (a product's sums) or as stored, dst as
+// stored (the second product's input).
+template <typename TS, typename T>
+__global__ void __launch_bounds__(256) tanh_rows_kernel(const TS *src, long long lds, T *dst, long long ldd, int cols, long long total) {
     pdl_wait();
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-    if (i < total) dst[i] = from_float<T>(tanhf(src[i]));
+    if (i >= total) return;
+    const long long t = i / cols;
+    const int j = (int)(i - t * cols);
+    dst[t * ldd + j] = from_float<T>(tanhf(to_float(src[t * lds + j])));
 }
 
-extern "C" int abk_tanh_rows(const float *src, void *dst, int dtype, long long total, void *stream) {
+extern "C" int abk_tanh_rows(const void *src, long long lds, int src_dtype, void *dst, long long ldd, int dtype, int n, int cols,
+                             void *stream) {
+    const long long total = (long long)n * cols;
     if (total <= 0) return 0;
     const dim3 grid((unsigned)((total + 255) / 256));
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == ABK_BF16) abk_launch(tanh_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, src, (__nv_bfloat16 *)dst, total);
-    else abk_launch(tanh_rows_kernel<float>, grid, dim3(256), 0, s, src, (float *)dst, total);
+    typedef __nv_bfloat16 bf;
+    if (dtype == ABK_BF16 && src_dtype == ABK_BF16)
+        abk_launch(tanh_rows_kernel<bf, bf>, grid, dim3(256), 0, s, (const bf *)src, lds, (bf *)dst, ldd, cols, total);
+    else if (dtype == ABK_BF16)
+        abk_launch(tanh_rows_kernel<float, bf>, grid, dim3(256), 0, s, (const float *)src, lds, (bf *)dst, ldd, cols, total);
+    else if (src_dtype == ABK_F32)
+        abk_launch(tanh_rows_kernel<float, float>, grid, dim3(256), 0, s, (const float *)src, lds, (float *)dst, ldd, cols, total);
+    else
+        ABK_REFUSE("tanh_rows: bfloat16 into float32 is not built");
     return ABK_LAUNCH_RESULT();
 }
 

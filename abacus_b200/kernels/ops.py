@@ -232,6 +232,22 @@ def gemm_rows(x, w, out, m=None):
                                   _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_rows")
 
 
+def gemm_rows_planes(x, w, out, block, m=None):
+    """Several products of a handful of rows in one launch: out[:m, i * block : (i + 1) * block] =
+    x[i, :m] . w[i * block : (i + 1) * block]^T for every run i of `block` rows of w (the last run may be shorter).
+    x [runs, rows, K] bfloat16 contiguous, w [N, K] bfloat16, out [rows, N] bfloat16 or float32; block a multiple of 16."""
+    _need_cuda(x, w, out)
+    lib = load_module("gemm_rows")
+    runs, rows, k = x.shape
+    m = rows if m is None else m
+    n = w.shape[0]
+    assert x.is_contiguous() and w.shape[1] == k and out.shape[1] == n and out.shape[0] >= m and -(-n // block) <= runs
+    assert x.dtype == w.dtype == torch.bfloat16 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib, lib.abk_gemm_rows_planes(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(1)),
+                                         _ll(w.stride(0)), _ll(out.stride(0)), _i(block), _ll(x.stride(0)), _stream()),
+           "gemm_rows_planes")
+
+
 def gemm_rows_swiglu(x, w_gate_up, act, m=None, block=None):
     """act[:m] = silu(x . gate^T) * (x . up^T) for m <= 64 rows, w_gate_up [2 I, K] holding gate and up rows in
     turns of `block` rows (by default all gates, then all ups): the feed-forward's first product and its
@@ -1338,11 +1354,12 @@ def token_shift(x, mu, last, out, batch):
 
 
 def tanh_rows(src, dst, n):
-    """dst[:n] = tanh(src[:n]): src float32, dst float32 or bfloat16, both contiguous and of one shape."""
+    """dst[:n] = tanh(src[:n]): src float32 or of dst's type, dst float32 or bfloat16, of one shape, rows of any pitch."""
     _need_cuda(src, dst)
     lib = load_module("wkv")
-    assert src.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous() and src.shape == dst.shape
-    _check(lib, lib.abk_tanh_rows(_p(src), _p(dst), _i(_dt(dst)), _ll(n * src.shape[1]), _stream()), "tanh_rows")
+    assert src.stride(1) == 1 and dst.stride(1) == 1 and src.shape[1] == dst.shape[1] and min(src.shape[0], dst.shape[0]) >= n
+    _check(lib, lib.abk_tanh_rows(_p(src), _ll(src.stride(0)), _i(_dt(src)), _p(dst), _ll(dst.stride(0)), _i(_dt(dst)), _i(n),
+                                  _i(src.shape[1]), _stream()), "tanh_rows")
 
 
 WKV_SEGMENT = 64        # tokens of a segment of the form for prompts

@@ -14,13 +14,17 @@ import torch
 from ..cache.need import CacheNeed
 from ..kernels import ops
 from .base import MIXERS, to_device
-from .linear import Linear
+from .linear import Linear, rows_kernel_wins
 
 _BLENDS = ("r", "k", "v", "g", "w")
 
 
 def _up8(n):
     return -(-n // 8) * 8
+
+
+def _up16(n):
+    return -(-n // 16) * 16
 
 
 @MIXERS.register("wkv")
@@ -34,9 +38,11 @@ class Wkv:
         if s.decay_rank < 1:
             raise ValueError(f"decay_rank {s.decay_rank}: the decay's two matrices have an inner size")
         self.size = s.n_heads * s.key_dim
-        self.at = {name: i * _up8(self.size) for i, name in enumerate(("r", "k", "v", "g"))}  # columns of the projections
-        self.width = 4 * _up8(self.size)
+        # columns of the projections r, k, v, gate, each from a multiple of 16 on, and behind them the decay's inner vector
+        self.block = _up16(self.size)
+        self.at = {name: i * self.block for i, name in enumerate(("r", "k", "v", "g", "w"))}
         self.rank = _up8(s.decay_rank)
+        self.width = 4 * self.block + self.rank
 
     def param_shapes(self):
         s = self.spec
@@ -49,20 +55,26 @@ class Wkv:
     def bind(self, params, ctx):
         s, self.ctx = self.spec, ctx
         self.mu = to_device(torch.stack([params[f"mu_{b}"].to(torch.float32) for b in _BLENDS]), ctx, torch.float32)
-        self.proj = {b: Linear(to_device(params[f"w{b}"], ctx, ctx.dtype)) for b in ("r", "k", "v", "g")}
-        # the decay's pair of matrices, their inner size padded with zeros to a multiple of 8
-        w1 = torch.zeros((self.rank, s.hidden), dtype=params["w1"].dtype)
-        w1[:s.decay_rank] = params["w1"]
+        # the five products that read the five blends, as one matrix: r, k, v, gate (each from a multiple of 16 rows on)
+        # and the first of the decay's pair (its inner size padded with zeros to a multiple of 8). A step of a few rows
+        # makes all five in one launch; else each is a product of its own on its rows of the matrix.
+        stacked = torch.zeros((self.width, s.hidden), dtype=params["wr"].dtype)
+        for b in ("r", "k", "v", "g"):
+            stacked[self.at[b]:self.at[b] + self.size] = params[f"w{b}"]
+        stacked[self.at["w"]:self.at["w"] + s.decay_rank] = params["w1"]
+        self.stacked = to_device(stacked, ctx, ctx.dtype)
+        self.proj = {b: Linear(self.stacked[self.at[b]:self.at[b] + self.size]) for b in ("r", "k", "v", "g")}
+        self.w1 = Linear(self.stacked[self.at["w"]:])
         w2 = torch.zeros((self.size, self.rank), dtype=params["w2"].dtype)
         w2[:, :s.decay_rank] = params["w2"]
-        self.w1, self.w2 = Linear(to_device(w1, ctx, ctx.dtype)), Linear(to_device(w2, ctx, ctx.dtype))
+        self.w2 = Linear(to_device(w2, ctx, ctx.dtype))
         self.w0 = to_device(params["w0"], ctx, torch.float32)
         self.bonus = to_device(params["bonus"].reshape(-1), ctx, torch.float32)
         self.out_norm = to_device(params["out_norm"], ctx, torch.float32)
         self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
 
     def step_weights(self):
-        return [self.mu, *(l.weight for l in self.proj.values()), self.w1.weight, self.w2.weight, self.w0, self.bonus,
+        return [self.mu, self.stacked, self.w2.weight, self.w0, self.bonus,
                 self.out_norm, self.o_proj.weight]
 
     def cache_need(self):
@@ -82,12 +94,18 @@ class Wkv:
         blends = ws.get("wkv_blends", (len(_BLENDS), n, s.hidden), dt)
         ops.token_shift(xn, self.mu, cache.states["wkv_last"], blends, batch)
         proj = ws.get("wkv_proj", (n, self.width), dt)
-        for i, b in enumerate(("r", "k", "v", "g")):
-            self.proj[b].forward(blends[i], proj[:, self.at[b]:self.at[b] + self.size], n)
-        sums = ws.get("wkv_inner_sums", (n, self.rank), torch.float32)
-        self.w1.forward(blends[4], sums, n)
         inner = ws.get("wkv_inner", (n, self.rank), dt)
-        ops.tanh_rows(sums, inner, n)
+        if (dt == torch.bfloat16 and self.rank <= self.block and rows_kernel_wins(n, self.stacked)
+                and ops.gemm_rows_takes(blends[0], self.stacked, proj, n)):
+            # a few rows: the five products in one launch, each run of the matrix's rows against its own blend
+            ops.gemm_rows_planes(blends, self.stacked, proj, self.block, n)
+            ops.tanh_rows(proj[:, self.at["w"]:], inner, n)
+        else:
+            for i, b in enumerate(("r", "k", "v", "g")):
+                self.proj[b].forward(blends[i], proj[:, self.at[b]:self.at[b] + self.size], n)
+            sums = ws.get("wkv_inner_sums", (n, self.rank), torch.float32)
+            self.w1.forward(blends[4], sums, n)
+            ops.tanh_rows(sums, inner, n)
         pre = ws.get("wkv_pre", (n, self.size), torch.float32)
         self.w2.forward(inner, pre, n)
         o = ws.get("wkv_o", (n, self.size), torch.float32)
