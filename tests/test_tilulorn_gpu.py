@@ -161,7 +161,8 @@ def _wkv_run(p, d, H, K, rank, dtype):
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("H,K,rank", [(2, 5, 3), (3, 16, 8), (1, 40, 6), (2, 64, 16), (2, 128, 5), (1, 200, 24)])
 def test_wkv_every_way(dtype, H, K, rank):
-    rng, rnd, d = np.random.default_rng(K), _rnd(dtype), 40
+    # (a width of 64: in bfloat16 a step of a few rows makes the five products in one launch; 40: each on its own)
+    rng, rnd, d = np.random.default_rng(K), _rnd(dtype), 64 if K in (16, 64) else 40
     p = _wkv(rng, d, H, K, rank, rnd)
     h = rnd(rng.standard_normal((150, d)))
     want, _ = plain.wkv(h.astype(np.float64), {"heads": H, "dim": K}, _f64(p), 1e-5, None)
@@ -308,6 +309,7 @@ def _window_run(p, d, m, dtype):
 @pytest.mark.parametrize("H,G,K,window,rotation", [
     (4, 2, 16, 40, tm.rot(5000.0, 8, 2.0)),       # half of each head turns, slowed
     (3, 3, 12, None, tm.rot(1000.0, 12)),         # every earlier key; a head that fits no vector
+    (4, 2, 16, None, tm.rot(1000.0, 16, 4.0, 64, 8.0, 1.0)),   # every earlier key, heads the tensor-core kernels take
     (1, 1, 20, 9, None),                          # no rotation
     (6, 1, 8, 64, tm.rot(20000.0, 8, 8.0, 32, 4.0, 1.0)),   # a window of a page; blended frequencies; one key head
     (8, 2, 64, 130, tm.rot(20000.0, 64, 2.0)),
@@ -412,6 +414,23 @@ def test_experts_picked_by_a_table(dtype, E, top, d, ff):
         got = np.concatenate(run.step([(None, h[:cut]), (None, h[cut:])] if cut else [(None, h)],
                                       tokens=[tokens[:cut], tokens[cut:]] if cut else [tokens]))
         _close(got, want, dtype, f"{top} of {E} experts, {rows} rows")
+
+
+def test_several_products_of_a_few_rows_in_one_launch():
+    """Runs of output features that each read an input of their own (the last run shorter), against float64."""
+    from abacus_b200.kernels import ops
+    rng = np.random.default_rng(12)
+    for rows, k, block, n in ((1, 64, 48, 48 * 4 + 8), (8, 320, 128, 128 * 4 + 16), (13, 1024, 1024, 4096 + 64)):
+        runs = -(-n // block)
+        x = tm.bf16_round(rng.standard_normal((runs, rows, k)))
+        w = tm.bf16_round(rng.standard_normal((n, k)) / np.sqrt(k))
+        want = np.concatenate([x[i].astype(np.float64) @ w[i * block:(i + 1) * block].astype(np.float64).T for i in range(runs)], axis=1)
+        xd, wd = torch.from_numpy(x).to(DEV).to(torch.bfloat16), torch.from_numpy(w).to(DEV).to(torch.bfloat16)
+        for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 8e-3)):
+            out = torch.full((rows, n), 7.0, dtype=out_dtype, device=DEV)
+            ops.gemm_rows_planes(xd, wd, out, block, rows)
+            torch.cuda.synchronize()
+            assert np.abs(out.float().cpu().numpy() - want).max() <= tol * max(np.abs(want).max(), 1.0), (rows, k, block, n, out_dtype)
 
 
 # ------------------------------------------------------------------ whole models through the engine
