@@ -82,7 +82,7 @@ def test_the_decays_inner_size_comes_from_the_tensors():
     assert [l.mixer.decay_rank for l in done.layers if l.type == "wkv"] == [5, 11]
 
 
-@pytest.mark.parametrize("rot", [tm.rot(10000.0, 16), tm.rot(20000.0, 64, 2.0), tm.rot(10000.0, 16, 4.0, 2048, 32.0, 1.0),
+@pytest.mark.parametrize("rot", [tm.rot(10000.0, 16), tm.rot(30000.0, 64, 3.0), tm.rot(50000.0, 16, 8.0, 1024, 16.0, 2.0),
                                  tm.rot(500.0, 8, 2.0, 16, 2.0, 0.5), tm.rot(1e6, 32, 8.0, 4096, 32.0, 1.0)])
 def test_the_tables_of_scaled_frequencies(rot):
     """The position part's tables against the frequencies written out here: plain, all slowed by a factor, and blended

@@ -219,7 +219,7 @@ def _latent_run(p, d, m, dtype):
     ((2, 10, 6, 7, 21, 9), tm.rot(100.0, 6)),                          # sizes that fit no vector; plain frequencies
     ((1, 12, 4, 12, 16, 16), None),                                     # no rotation at all
     ((4, 8, 16, 8, 32, 24), tm.rot(10000.0, 12, 3.0)),                  # part of the rotated part turns, slowed
-    ((5, 32, 16, 40, 64, 48), tm.rot(10000.0, 16, 4.0, 2048, 32.0, 1.0)),
+    ((5, 32, 16, 40, 64, 48), tm.rot(50000.0, 16, 8.0, 1024, 16.0, 2.0)),
 ])
 def test_latent_attention_with_query_latents_and_gated_heads_every_way(dtype, sizes, rotation):
     H, K, R, V, rank, qr = sizes
@@ -312,7 +312,7 @@ def _window_run(p, d, m, dtype):
     (4, 2, 16, None, tm.rot(1000.0, 16, 4.0, 64, 8.0, 1.0)),   # every earlier key, heads the tensor-core kernels take
     (1, 1, 20, 9, None),                          # no rotation
     (6, 1, 8, 64, tm.rot(20000.0, 8, 8.0, 32, 4.0, 1.0)),   # a window of a page; blended frequencies; one key head
-    (8, 2, 64, 130, tm.rot(20000.0, 64, 2.0)),
+    (8, 2, 64, 130, tm.rot(30000.0, 64, 3.0)),
     (2, 2, 7, 5, tm.rot(300.0, 4)),
 ])
 def test_attention_with_values_that_are_keys_a_window_and_a_sink_every_way(dtype, H, G, K, window, rotation):
@@ -331,7 +331,7 @@ def test_attention_with_values_that_are_keys_a_window_and_a_sink_every_way(dtype
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("window", [5, 64, 72, 130])
+@pytest.mark.parametrize("window", [5, 64, 80, 130])
 def test_one_loud_key_just_inside_and_just_outside_the_window(window, dtype):
     """A key made loud for one query alone (q reads one part of the input row, k another; the norm over the whole row
     keeps directions): the oldest key the window still holds, the first it has dropped, keys on both sides of a page's
