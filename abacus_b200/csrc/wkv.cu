@@ -206,9 +206,27 @@ __device__ __forceinline__ void wkv_segment(const int *seq_start, int n_seqs, in
 
 // N tokens of one thread's share: r, k, w point at the thread's channels of the first token (tokens `pitch` floats
 // apart), v at its column's value (tokens `v_pitch` apart); the column's output goes to out if `writes`.
-template <int DPT, int PARTS, int N>
+// SUMS: the state alone moves (a segment's own sum): no r, no output.
+template <int DPT, int PARTS, int N, bool SUMS>
 __device__ __forceinline__ void wkv_tokens(float *s, const float *u, const float *r, const float *k, const float *w, int pitch,
                                            const float *v, int v_pitch, bool writes, float *out, long long out_pitch) {
+    if constexpr (SUMS) {
+        float vv[N];
+#pragma unroll
+        for (int n = 0; n < N; n++) vv[n] = v[n * v_pitch];
+#pragma unroll
+        for (int i = 0; i < DPT / 4; i++) {
+            float4 kk[N], ww[N];
+#pragma unroll
+            for (int n = 0; n < N; n++) kk[n] = *(const float4 *)(k + n * pitch + 4 * i), ww[n] = *(const float4 *)(w + n * pitch + 4 * i);
+#pragma unroll
+            for (int n = 0; n < N; n++) {
+                s[4 * i] = fmaf(ww[n].x, s[4 * i], kk[n].x * vv[n]), s[4 * i + 1] = fmaf(ww[n].y, s[4 * i + 1], kk[n].y * vv[n]);
+                s[4 * i + 2] = fmaf(ww[n].z, s[4 * i + 2], kk[n].z * vv[n]), s[4 * i + 3] = fmaf(ww[n].w, s[4 * i + 3], kk[n].w * vv[n]);
+            }
+        }
+        return;
+    }
     float vv[N], o[N];
 #pragma unroll
     for (int n = 0; n < N; n++) vv[n] = v[n * v_pitch], o[n] = 0.0f;
@@ -242,7 +260,12 @@ __device__ __forceinline__ void wkv_tokens(float *s, const float *u, const float
 
 // DPT key channels a thread, PARTS threads a value column (DPT * PARTS >= dim); a CTA has COLS columns and stages TOK
 // tokens at a time.
-template <typename T, int DPT, int PARTS, int COLS, int TOK>
+// The decay from its pre-activation: to the last bit where the model is float32; where the model's operands are bfloat16
+// numbers, by the special-function unit (a few units in the last place of float32, in float32 arithmetic).
+template <typename T> __device__ __forceinline__ float wkv_decay(float z) { return expf(-expf(z)); }
+template <> __device__ __forceinline__ float wkv_decay<__nv_bfloat16>(float z) { return __expf(-__expf(z)); }
+
+template <typename T, int DPT, int PARTS, int COLS, int TOK, bool SUMS>
 __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
     constexpr int DP = DPT * PARTS;             // key channels, padded
     constexpr int PITCH = PARTS * (DPT + 4);    // a token's channels in shared memory: a part's run, then 4 floats of
@@ -293,7 +316,8 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
             const int tok = (tid + it * THREADS) / DP;
             const long long row = row0 + c0 + (tok < cnt ? tok : cnt - 1);
             const T *r = proj + row * p.ld + my_ch;
-            rr[it] = r[p.r_at], rk[it] = r[p.k_at], rz[it] = p.pre[row * hk + my_ch];
+            if (!SUMS) rr[it] = r[p.r_at];
+            rk[it] = r[p.k_at], rz[it] = p.pre[row * hk + my_ch];
         }
 #pragma unroll
         for (int it = 0; it < PER_V; it++) {
@@ -311,8 +335,9 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
             if (it * THREADS >= cnt * DP) break;
             const int tok = (tid + it * THREADS) / DP, at = (my_d / DPT) * (DPT + 4) + my_d % DPT;
             const bool in = tok < cnt && my_d < p.dim;
-            const float w = expf(-expf(rz[it] + my_w0));
-            r_s[tok][at] = in ? to_float(rr[it]) : 0.0f, k_s[tok][at] = in ? to_float(rk[it]) : 0.0f, w_s[tok][at] = w;
+            const float w = wkv_decay<T>(rz[it] + my_w0);
+            if (!SUMS) r_s[tok][at] = in ? to_float(rr[it]) : 0.0f;
+            k_s[tok][at] = in ? to_float(rk[it]) : 0.0f, w_s[tok][at] = w;
             if (in) decayed *= w;
         }
 #pragma unroll
@@ -329,9 +354,9 @@ __global__ void __launch_bounds__(PARTS * COLS, 2) wkv_scan_kernel(WkvScan p) {
         const bool writes = part == 0 && col < p.dim && p.phase != 1;
         int tok = 0;
         for (; tok + 4 <= cnt; tok += 4)
-            wkv_tokens<DPT, PARTS, 4>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
+            wkv_tokens<DPT, PARTS, 4, SUMS>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
         for (; tok < cnt; tok++)
-            wkv_tokens<DPT, PARTS, 1>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
+            wkv_tokens<DPT, PARTS, 1, SUMS>(s, u, &r_s[tok][at], &k_s[tok][at], &w_s[tok][at], PITCH, &v_s[tok][vc], COLS, writes, out + tok * hk, hk);
     }
     if (p.phase == 2) return;  // (the states between segments are wkv_segment_prefix's)
 #pragma unroll
@@ -400,18 +425,18 @@ extern "C" int abk_wkv_scan(const void *proj, long long ld, int dtype, int r_at,
     cudaStream_t s = (cudaStream_t)stream;
     const int cols = dim <= 32 ? 32 : 16;  // value columns a CTA has
     dim3 grid((dim + cols - 1) / cols, n_heads, chunk > 0 ? segments : n_seqs);
-#define WS_LAUNCH(T)                                                                                  \
-    do {                                                                                              \
-        if (dim <= 16) abk_launch(wkv_scan_kernel<T, 4, 4, 32, 16>, grid, dim3(128), 0, s, p);        \
-        else if (dim <= 32) abk_launch(wkv_scan_kernel<T, 8, 4, 32, 16>, grid, dim3(128), 0, s, p);   \
-        else if (dim <= 64) abk_launch(wkv_scan_kernel<T, 8, 8, 16, 16>, grid, dim3(128), 0, s, p);   \
-        else if (dim <= 128) abk_launch(wkv_scan_kernel<T, 8, 16, 16, 16>, grid, dim3(256), 0, s, p); \
-        else abk_launch(wkv_scan_kernel<T, 16, 16, 16, 8>, grid, dim3(256), 0, s, p);                 \
+#define WS_LAUNCH(T, SUMS)                                                                                  \
+    do {                                                                                                    \
+        if (dim <= 16) abk_launch(wkv_scan_kernel<T, 4, 4, 32, 16, SUMS>, grid, dim3(128), 0, s, p);        \
+        else if (dim <= 32) abk_launch(wkv_scan_kernel<T, 8, 4, 32, 16, SUMS>, grid, dim3(128), 0, s, p);   \
+        else if (dim <= 64) abk_launch(wkv_scan_kernel<T, 8, 8, 16, 16, SUMS>, grid, dim3(128), 0, s, p);   \
+        else if (dim <= 128) abk_launch(wkv_scan_kernel<T, 8, 16, 16, 16, SUMS>, grid, dim3(256), 0, s, p); \
+        else abk_launch(wkv_scan_kernel<T, 16, 16, 16, 8, SUMS>, grid, dim3(256), 0, s, p);                 \
     } while (0)
     if (chunk > 0) {  // the segments' sums, the states between them, the segments' outputs
         p.phase = 1;
-        if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16);
-        else WS_LAUNCH(float);
+        if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16, true);
+        else WS_LAUNCH(float, true);
         int rc = ABK_LAUNCH_RESULT();
         if (rc) return rc;
         abk_launch(wkv_segment_prefix_kernel, dim3((dim * dim + 255) / 256, n_heads, n_seqs), dim3(256), 0, s, sums, prods, state,
@@ -420,8 +445,8 @@ extern "C" int abk_wkv_scan(const void *proj, long long ld, int dtype, int r_at,
         if (rc) return rc;
         p.phase = 2;
     }
-    if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16);
-    else WS_LAUNCH(float);
+    if (dtype == ABK_BF16) WS_LAUNCH(__nv_bfloat16, false);
+    else WS_LAUNCH(float, false);
 #undef WS_LAUNCH
     return ABK_LAUNCH_RESULT();
 }
