@@ -35,6 +35,8 @@ struct AttnSplit {
     int n_parts;
     int values_in_keys;  // a value is the first v_dim elements of its key row (one pool)
     int one_kv;          // the cache has one kv head; n_kv_heads counts runs of query heads that a CTA takes together
+    const void *gate;    // null, or a gate per token and head (of q's type, at gate + t * ldg + h): the head's output is
+    long long ldg;       // multiplied by its sigmoid where the parts are folded
 };
 
 // (first key of the window, number of kept first keys before it, number of visible keys) of a token at pos
@@ -340,8 +342,9 @@ template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_fo
         if (tid < vd) a = fmaf(part[tid], w, a);
         if (tid + AS_THREADS < vd) b = fmaf(part[tid + AS_THREADS], w, b);
     }
-    if (tid < vd) out[tid] = from_float<T>(a / l);
-    if (tid + AS_THREADS < vd) out[tid + AS_THREADS] = from_float<T>(b / l);
+    const float g = p.gate ? 1.0f / (1.0f + expf(-to_float(((const T *)p.gate)[(long long)t * p.ldg + h]))) : 1.0f;
+    if (tid < vd) out[tid] = from_float<T>(a / l * g);
+    if (tid + AS_THREADS < vd) out[tid + AS_THREADS] = from_float<T>(b / l * g);
 }
 
 // max_keys: an upper bound of the keys any row of the step sees (its position + 1, or window + keep_first);
@@ -351,7 +354,7 @@ static int attention_split(int values_in_keys, int chunk, float softcap, const v
                                    const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
                                    const void *k_pool, const void *v_pool, const int *page_table, int table_width,
                                    int ring_pages, int pinned_pages, int tokens_per_page, int max_keys, float *parts,
-                                   long long parts_floats, void *stream) {
+                                   long long parts_floats, const void *gate, long long ldg, void *stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim > AS_MAX_DIM || head_dim % 8 || head_dim < 8) ABK_REFUSE("attention_split: head_dim %d is not a multiple of 8 up to %d", head_dim, AS_MAX_DIM);
     if (v_dim < 1 || v_dim > AS_MAX_DIM) ABK_REFUSE("attention_split: value size %d is not 1 to %d", v_dim, AS_MAX_DIM);
@@ -376,7 +379,7 @@ static int attention_split(int values_in_keys, int chunk, float softcap, const v
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
     p.v_cache = p.cache;
     p.n_parts = (max_keys + AS_THREADS - 1) / AS_THREADS;
-    p.values_in_keys = values_in_keys, p.one_kv = one_kv;
+    p.values_in_keys = values_in_keys, p.one_kv = one_kv, p.gate = gate, p.ldg = ldg;
     if (values_in_keys && v_dim > head_dim) ABK_REFUSE("attention_split: values of %d inside keys of %d", v_dim, head_dim);
     if (p.n_parts > 65535) ABK_REFUSE("attention_split: %d keys are more than a grid takes", max_keys);
     if ((long long)n_tokens * n_heads * p.n_parts * (v_dim + 2) > parts_floats)
@@ -433,10 +436,11 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
                                    const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
                                    const void *k_pool, const void *v_pool, const int *page_table, int table_width,
                                    int ring_pages, int pinned_pages, int tokens_per_page, int max_keys, float *parts,
-                                   long long parts_floats, int chunk, float softcap, void *stream) {
+                                   long long parts_floats, int chunk, float softcap, const void *gate, long long ldg,
+                                   void *stream) {
     return attention_split(0, chunk, softcap, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first,
                            sink, token_seq, token_pos, seq_slot, k_pool, v_pool, page_table, table_width, ring_pages,
-                           pinned_pages, tokens_per_page, max_keys, parts, parts_floats, stream);
+                           pinned_pages, tokens_per_page, max_keys, parts, parts_floats, gate, ldg, stream);
 }
 
 // Keys that carry their values (a value is the first v_dim elements of its key row; one pool): attention over shared
@@ -449,5 +453,5 @@ extern "C" int abk_attention_split_values_in_keys(const void *q, long long q_row
                                                   long long parts_floats, void *stream) {
     return attention_split(1, 0, 0.0f, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, 0, 0, sink,
                            token_seq, token_pos, seq_slot, k_pool, k_pool, page_table, table_width, 0, 0, tokens_per_page,
-                           max_keys, parts, parts_floats, stream);
+                           max_keys, parts, parts_floats, nullptr, 0, stream);
 }

@@ -55,7 +55,7 @@ template <int NT, int TILE, bool GATED, typename TO>
 __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bfloat16 *__restrict__ x,
                                                                  const __nv_bfloat16 *__restrict__ w, TO *__restrict__ out,
                                                                  int M, int N, int K, long long ldx, long long ldw,
-                                                                 long long ldo, int block, long long x_plane) {
+                                                                 long long ldo, int block, long long x_plane, int tanh_from) {
     __shared__ float part[ROWS_WARPS][16][8 * NT + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     const int ranks = (int)tc::cluster_size(), rank = (int)tc::cluster_rank();  // the cluster splits K
@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
                     }
 #pragma unroll
                     for (int c = 1; c < 8; c++) sum += v[c];
+                    if (n0 + row >= tanh_from) sum = tanhf(sum);
                     out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
                 }
             }
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
                 sum = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(up));
                 sum = silu_mul_fast(sum, up);
             }
+            if (!GATED && n0 + row >= tanh_from) sum = tanhf(sum);  // (tanh_from beyond N: no feature)
             out[(long long)token * ldo + n0 + row] = from_float<TO>(sum);
         }
     }
@@ -170,8 +172,9 @@ __global__ void __launch_bounds__(ROWS_THREADS) gemm_rows_kernel(const __nv_bflo
 // x [M, K], w [N, K] bfloat16 (row pitches ldx, ldw in elements); out [M, N] bfloat16 or float32.
 // M <= 16, K a multiple of 32, rows 16-byte aligned. block > 0: output features [i * block, (i + 1) * block) read
 // x + i * x_plane (block a multiple of 16; the last run may be shorter).
+// tanh_from: output features from there on pass tanh (N or more: none).
 static int gemm_rows_launch(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
-                            long long ldw, long long ldo, int block, long long x_plane, void *stream) {
+                            long long ldw, long long ldo, int block, long long x_plane, int tanh_from, void *stream) {
     if (M <= 0 || N <= 0) return 0;
     if (block < 0 || block % 16 || x_plane % 8) ABK_REFUSE("gemm_rows: runs of %d features, inputs %lld elements apart", block, x_plane);
     if (M > 64) ABK_REFUSE("gemm_rows: %d rows are more than 64", M);
@@ -190,7 +193,7 @@ static int gemm_rows_launch(const void *x, const void *w, void *out, int out_dty
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define ROWS_LAUNCH(NT, TILE, TO)                                                                                     \
     abk_launch_clusters(gemm_rows_kernel<NT, TILE, false, TO>, grid, dim3(ROWS_THREADS), 0, s, ranks, xb, wb, (TO *)out, M, \
-                        N, K, ldx, ldw, ldo, block, x_plane)
+                        N, K, ldx, ldw, ldo, block, x_plane, tanh_from)
 #define ROWS_BY_M(TO)                                                                     \
     if (M <= 8) { if (narrow) ROWS_LAUNCH(1, 8, TO); else ROWS_LAUNCH(1, 16, TO); }       \
     else if (M <= 16) { if (narrow) ROWS_LAUNCH(2, 8, TO); else ROWS_LAUNCH(2, 16, TO); } \
@@ -204,15 +207,15 @@ static int gemm_rows_launch(const void *x, const void *w, void *out, int out_dty
 
 extern "C" int abk_gemm_rows(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
                              long long ldw, long long ldo, void *stream) {
-    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, 0, 0, stream);
+    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, 0, 0, 0x7fffffff, stream);
 }
 
 // Several products of one launch: out[:, i * block : (i + 1) * block] = x_i . w[i * block : (i + 1) * block]^T with
-// x_i = x + i * x_plane (each [M, K] with pitch ldx).
+// x_i = x + i * x_plane (each [M, K] with pitch ldx). Output features from tanh_from on (negative: none) pass tanh.
 extern "C" int abk_gemm_rows_planes(const void *x, const void *w, void *out, int out_dtype, int M, int N, int K, long long ldx,
-                                    long long ldw, long long ldo, int block, long long x_plane, void *stream) {
+                                    long long ldw, long long ldo, int block, long long x_plane, int tanh_from, void *stream) {
     if (block <= 0) ABK_REFUSE("gemm_rows_planes: runs of %d features", block);
-    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, block, x_plane, stream);
+    return gemm_rows_launch(x, w, out, out_dtype, M, N, K, ldx, ldw, ldo, block, x_plane, tanh_from < 0 ? 0x7fffffff : tanh_from, stream);
 }
 
 // act[M, N] = silu(x . w_gate^T) * (x . w_up^T) where w [2 N, K] holds gate and up rows in turns of `block`
@@ -229,7 +232,7 @@ extern "C" int abk_gemm_rows_swiglu(const void *x, const void *w, void *act, int
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x, *wb = (const __nv_bfloat16 *)w;
 #define GATED_LAUNCH(NT) \
-    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo, block, 0LL)
+    abk_launch(gemm_rows_kernel<NT, 8, true, __nv_bfloat16>, grid, dim3(ROWS_THREADS), 0, s, xb, wb, (__nv_bfloat16 *)act, M, N, K, ldx, ldw, ldo, block, 0LL, 0x7fffffff)
     if (M <= 8) GATED_LAUNCH(1);
     else if (M <= 16) GATED_LAUNCH(2);
     else if (M <= 32) GATED_LAUNCH(4);

@@ -156,7 +156,8 @@ extern "C" int abk_columns_norm(const void *src, long long lds, void *dst, long 
 template <typename T>
 __global__ void __launch_bounds__(128) head_product_kernel(const T *__restrict__ x, long long ldx, int x_head,
                                                            const T *__restrict__ w, T *__restrict__ out, long long ldo,
-                                                           int o_head, int n, int in, int outs) {
+                                                           int o_head, int n, int in, int outs, const T *__restrict__ gate,
+                                                           long long ldg) {
     extern __shared__ __align__(16) float hp_x[];  // [HP_ROWS][in4], in4 = in rounded up to 4
     const int h = blockIdx.y, r0 = blockIdx.z * HP_ROWS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = n - r0 < HP_ROWS ? n - r0 : HP_ROWS;
@@ -177,15 +178,20 @@ __global__ void __launch_bounds__(128) head_product_kernel(const T *__restrict__
             float acc = 0.0f;
             lane_dots<1>(wr, 0, hp_x + r * in4, in, lane, vec, &acc);
             acc = warp_sum(acc);
-            if (lane == 0) out[(long long)(r0 + r) * ldo + (long long)h * o_head + o] = from_float<T>(acc);
+            if (lane == 0) {
+                if (gate) acc *= 1.0f / (1.0f + expf(-to_float(gate[(long long)(r0 + r) * ldg + h])));  // a gate per head
+                out[(long long)(r0 + r) * ldo + (long long)h * o_head + o] = from_float<T>(acc);
+            }
         }
     }
 }
 
 // x element (t, h, i) at x + t * ldx + h * x_head + i; w [heads][outs][in]; out element (t, h, o) at
-// out + t * ldo + h * o_head + o. x, w and out are of one type.
+// out + t * ldo + h * o_head + o. x, w and out are of one type. gate (null: none): head h of row t is multiplied by
+// sigmoid(gate[t * ldg + h]).
 extern "C" int abk_head_product(const void *x, long long ldx, int x_head, const void *w, void *out, long long ldo,
-                                int o_head, int dtype, int n, int heads, int in, int outs, void *stream) {
+                                int o_head, int dtype, int n, int heads, int in, int outs, const void *gate, long long ldg,
+                                void *stream) {
     if (n <= 0 || heads <= 0 || outs <= 0) return 0;
     if (in < 1 || in > 4096) ABK_REFUSE("head_product: an inner size of %d is not 1 to 4096", in);
     const long long row_tiles = ((long long)n + HP_ROWS - 1) / HP_ROWS;
@@ -199,14 +205,14 @@ extern "C" int abk_head_product(const void *x, long long ldx, int x_head, const 
             if (e != cudaSuccess) return (int)e;
         }
         abk_launch(head_product_kernel<__nv_bfloat16>, grid, dim3(128), smem, s, (const __nv_bfloat16 *)x, ldx, x_head,
-                   (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, ldo, o_head, n, in, outs);
+                   (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, ldo, o_head, n, in, outs, (const __nv_bfloat16 *)gate, ldg);
     } else {
         if (smem > 48 * 1024) {
             cudaError_t e = abk_allow_shared_memory((const void *)head_product_kernel<float>, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
         abk_launch(head_product_kernel<float>, grid, dim3(128), smem, s, (const float *)x, ldx, x_head, (const float *)w,
-                   (float *)out, ldo, o_head, n, in, outs);
+                   (float *)out, ldo, o_head, n, in, outs, (const float *)gate, ldg);
     }
     return ABK_LAUNCH_RESULT();
 }

@@ -232,10 +232,11 @@ def gemm_rows(x, w, out, m=None):
                                   _ll(w.stride(0)), _ll(out.stride(0)), _stream()), "gemm_rows")
 
 
-def gemm_rows_planes(x, w, out, block, m=None):
+def gemm_rows_planes(x, w, out, block, m=None, tanh_from=None):
     """Several products of a handful of rows in one launch: out[:m, i * block : (i + 1) * block] =
     x[i, :m] . w[i * block : (i + 1) * block]^T for every run i of `block` rows of w (the last run may be shorter).
-    x [runs, rows, K] bfloat16 contiguous, w [N, K] bfloat16, out [rows, N] bfloat16 or float32; block a multiple of 16."""
+    x [runs, rows, K] bfloat16 contiguous, w [N, K] bfloat16, out [rows, N] bfloat16 or float32; block a multiple of 16.
+    tanh_from: output features from there on are tanh of their sums."""
     _need_cuda(x, w, out)
     lib = load_module("gemm_rows")
     runs, rows, k = x.shape
@@ -244,7 +245,8 @@ def gemm_rows_planes(x, w, out, block, m=None):
     assert x.is_contiguous() and w.shape[1] == k and out.shape[1] == n and out.shape[0] >= m and -(-n // block) <= runs
     assert x.dtype == w.dtype == torch.bfloat16 and w.stride(1) == 1 and out.stride(1) == 1
     _check(lib, lib.abk_gemm_rows_planes(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(1)),
-                                         _ll(w.stride(0)), _ll(out.stride(0)), _i(block), _ll(x.stride(0)), _stream()),
+                                         _ll(w.stride(0)), _ll(out.stride(0)), _i(block), _ll(x.stride(0)),
+                                         _i(-1 if tanh_from is None else tanh_from), _stream()),
            "gemm_rows_planes")
 
 
@@ -371,13 +373,15 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
 
 
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None,
-              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False, row=None, chunk=None, softcap=None):
+              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False, row=None, chunk=None, softcap=None,
+              gate=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
     (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel.
     prepare: see attention_decode (only where attention_decode_prepares() said yes for this step).
     v_dim, keep_first, sink, exact_weights: see attention_generic and attention_window; the kernels for plain heads
-    take none of them."""
+    take none of them. gate: a gate per row and head (see attention_split) that the kernel may apply itself: returns True
+    if it did (else the caller applies it)."""
     if chunk or softcap:  # the general kernel knows chunks and capped scores, and the prompt kernel with float32 weights
         assert prepare is None, "q, k and v must be prepared before this kernel"
         if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
@@ -399,8 +403,8 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
         if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
                 and n_heads // n_kv_heads <= 16 and head_dim % 8 == 0):
             attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=v_dim,
-                            keep_first=keep_first, sink=sink, row=row)  # one token a sequence: split along the keys
-            return
+                            keep_first=keep_first, sink=sink, row=row, gate=gate)  # one token a sequence: split along the keys
+            return gate is not None
         if (exact_weights and not batch.is_decode and not batch.any_continuation
                 and attention_window_takes(qkv, head_dim, v_dim or head_dim, n_heads, n_kv_heads, row)):
             attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=v_dim,
@@ -454,11 +458,13 @@ def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
 
 
 def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=None, keep_first=0,
-                    sink=None, row=None, max_keys=None, chunk=None, softcap=None):
+                    sink=None, row=None, max_keys=None, chunk=None, softcap=None, gate=None):
     """One new token per sequence against the paged cache with the general options (see attention_generic), split
     along the keys into parts of 128 that a second kernel folds (csrc/attention_split.cu); softmax weights float32.
-    max_keys bounds the keys a row sees (by default the window and its kept keys, or the step's position bound)."""
-    _need_cuda(qkv, out, sink)
+    max_keys bounds the keys a row sees (by default the window and its kept keys, or the step's position bound).
+    gate (of qkv's type, [rows, >= heads]): head h of row t is multiplied by sigmoid(gate[t, h]) where the parts are folded."""
+    _need_cuda(qkv, out, sink, gate)
+    assert gate is None or (gate.dtype == qkv.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
     lib = load_module("attention_split")
     n, vd = batch.n_rows, v_dim or head_dim
     heads_size = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
@@ -480,7 +486,7 @@ def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batc
         _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot),
         _p(cache.k), _p(cache.v), _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages),
         _i(cache.pinned_pages), _i(cache.tokens_per_page), _i(max_keys), _p(parts), _ll(parts.numel()), _i(chunk or 0),
-        _f(softcap or 0.0), _stream()),
+        _f(softcap or 0.0), _p(gate), _ll(gate.stride(0) if gate is not None else 0), _stream()),
         "attention_split", kernels=2)
 
 
@@ -969,17 +975,20 @@ def latent_prep(proj, down_at, n_heads, dim, rot, rank, rot_dims, norm_w, eps, c
         _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _stream()), "latent_prep")
 
 
-def head_product(x, x_head, w, out, o_head, n):
+def head_product(x, x_head, w, out, o_head, n, gate=None):
     """out[t, h * o_head + o] = sum_i w[h, o, i] * x[t, h * x_head + i] for t < n: a product per head with a matrix of
-    its own, w [heads, outs, in]; x, w and out of one type, rows of any pitch."""
+    its own, w [heads, outs, in]; x, w and out of one type, rows of any pitch. gate (of their type, [rows, >= heads]):
+    head h of row t is multiplied by sigmoid(gate[t, h])."""
     _need_cuda(x, w, out)
     lib = load_module("latent")
     heads, outs, inner = w.shape
     assert x.dtype == w.dtype == out.dtype and w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1
     assert x.shape[0] >= n and out.shape[0] >= n and x_head >= inner and o_head >= outs
     assert x.shape[1] >= (heads - 1) * x_head + inner and out.shape[1] >= (heads - 1) * o_head + outs
+    assert gate is None or (gate.dtype == x.dtype and gate.stride(1) == 1 and gate.shape[1] >= heads and gate.shape[0] >= n)
     _check(lib, lib.abk_head_product(_p(x), _ll(x.stride(0)), _i(x_head), _p(w), _p(out), _ll(out.stride(0)), _i(o_head),
-                                     _i(_dt(x)), _i(n), _i(heads), _i(inner), _i(outs), _stream()), "head_product")
+                                     _i(_dt(x)), _i(n), _i(heads), _i(inner), _i(outs), _p(gate),
+                                     _ll(gate.stride(0) if gate is not None else 0), _stream()), "head_product")
 
 
 def latent_rows(cache, rows, count, batch):

@@ -202,11 +202,12 @@ class Attention:
             raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
                                     "and only with keys of its own")
         mine = batch.plan.get(self.lists.name)
-        ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
+        gates = ws.get("qkv_proj", (n, self.proj_row), self.ctx.dtype)[:, self.gate_at:] if s.head_gate else None
+        gated = ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
                       from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare,
                       v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights,
-                      row=self.row if self.general else None, chunk=s.chunk, softcap=s.softcap)
-        if s.head_gate:  # head h's output times sigmoid(g_h . x)
-            ops.gate_heads(att, ws.get("qkv_proj", (n, self.proj_row), self.ctx.dtype)[:, self.gate_at:], s.n_heads, self.v_dim, n)
+                      row=self.row if self.general else None, chunk=s.chunk, softcap=s.softcap, gate=gates)
+        if s.head_gate and not gated:  # head h's output times sigmoid(g_h . x), where the attention kernel did not do it
+            ops.gate_heads(att, gates, s.n_heads, self.v_dim, n)
         self.o_proj.forward(att, out, n)
         return out

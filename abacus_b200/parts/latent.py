@@ -140,6 +140,7 @@ class LatentAttention:
             self.in_proj.forward(xn, proj, n)
         att = ws.get("att", (n, s.n_heads * s.v_head_dim), dt)
         kv = cache.kv
+        gated = False
         if self.full_size_takes(batch):
             heads_size = 2 * self.q_size + s.n_heads * s.v_head_dim
             qkv = ws.get("latent_qkv", (n, _up8(heads_size)), dt)
@@ -160,8 +161,10 @@ class LatentAttention:
             ops.head_product(proj, self.per_head, self.uk_t, q_lat, self.row, n)
             mixed = ws.get("latent_mixed", (n, s.n_heads * s.rank), dt)
             ops.attention_values_in_keys(q_lat, mixed, s.n_heads, self.row, s.rank, s.scale, batch, kv, self.sink, ws)
-            ops.head_product(mixed, s.rank, self.uv, att, s.v_head_dim, n)
-        if s.head_gate:  # head h's output times sigmoid(g_h . x)
+            # (head h's output times sigmoid(g_h . x) where the values leave the latent space)
+            ops.head_product(mixed, s.rank, self.uv, att, s.v_head_dim, n, gate=proj[:, self.gate_at:] if s.head_gate else None)
+            gated = True
+        if s.head_gate and not gated:  # head h's output times sigmoid(g_h . x)
             ops.gate_heads(att, proj[:, self.gate_at:], s.n_heads, s.v_head_dim, n)
         self.o_proj.forward(att, out, n)
         return out

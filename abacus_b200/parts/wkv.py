@@ -98,8 +98,9 @@ class Wkv:
         if (dt == torch.bfloat16 and self.rank <= self.block and rows_kernel_wins(n, self.stacked)
                 and ops.gemm_rows_takes(blends[0], self.stacked, proj, n)):
             # a few rows: the five products in one launch, each run of the matrix's rows against its own blend
-            ops.gemm_rows_planes(blends, self.stacked, proj, self.block, n)
-            ops.tanh_rows(proj[:, self.at["w"]:], inner, n)
+            # (the decay's inner vector passes tanh where its product stores it)
+            ops.gemm_rows_planes(blends, self.stacked, proj, self.block, n, tanh_from=self.at["w"])
+            inner = proj[:, self.at["w"]:]
         else:
             for i, b in enumerate(("r", "k", "v", "g")):
                 self.proj[b].forward(blends[i], proj[:, self.at[b]:self.at[b] + self.size], n)
